@@ -1,0 +1,192 @@
+/* pat_b200 - C ABI of the B200 prefix-aware decode-attention path.
+ *
+ * Plain C, no torch types: pointers, sizes, strides (in elements) and a CUDA
+ * stream handle.  Every function returns 0 on success or a negative pat_status
+ * (pat_b200_strerror gives the text); nothing throws, exits or traps.
+ *
+ * Each entry point names the reference interface it replaces
+ * (paths relative to the reference checkout).
+ */
+#ifndef PAT_B200_H_
+#define PAT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pat_status {
+    PAT_OK = 0,
+    PAT_ERR_BAD_ARGUMENT = -1,
+    PAT_ERR_EMPTY_QUERY_BOX = -2,    /* Python semantics: IndexError in the reference */
+    PAT_ERR_ZERO_QUERIES_PER_BOX = -3, /* Python semantics: max M < HRatio */
+    PAT_ERR_UNKNOWN_BUCKET = -4,     /* Python semantics: KeyError in the reference */
+    PAT_ERR_NOT_BUILT = -5,
+    PAT_ERR_BAD_PLAN = -10,          /* plan tables inconsistent (index out of range ...) */
+    PAT_ERR_UNSUPPORTED = -11,       /* dtype / head_dim / head ratio / alignment not supported */
+    PAT_ERR_WORKSPACE = -12,         /* workspace too small or missing */
+    PAT_ERR_CUDA = -13,              /* a CUDA runtime or driver call failed */
+    PAT_ERR_NO_DEVICE_CODE = -14,    /* the GPU is not an sm_100 part */
+    PAT_ERR_TOO_LARGE = -15          /* size beyond a fixed limit */
+} pat_status;
+
+const char* pat_b200_strerror(int status);
+/* Library version, bumped on any ABI change. */
+int pat_b200_abi_version(void);
+
+/* ------------------------------------------------------------------------- *
+ * Scheduler: radix tree over physical page ids + tile-plan packer (host).
+ * Replaces class PrefixTree of csrc/prefix_tree.h:63-324 as bound by
+ * csrc/bindings.cpp:100-146 (PrefixTreeCPP), and can also reproduce
+ * prefix_attn/prefix_tree.py:47-616 bit for bit.
+ * ------------------------------------------------------------------------- */
+typedef struct pat_tree pat_tree;
+
+enum { PAT_SEMANTICS_PYTHON = 0, PAT_SEMANTICS_CPP = 1 };
+
+/* csrc/bindings.cpp:101  PrefixTreeCPP(block_size) */
+pat_tree* pat_tree_create(int block_size, int semantics);
+void pat_tree_destroy(pat_tree* t);
+
+/* csrc/bindings.cpp:103-126 / csrc/prefix_tree.h:84-101  build_radix_tree(seq_lens, block_table):
+ * padded int32 table [num_seqs, row_stride]; row i is cut to ceil(seq_lens[i]/block_size) pages.
+ * The table is copied; the caller may free it as soon as the call returns. */
+int pat_tree_build(pat_tree* t, const int32_t* seq_lens, const int32_t* block_table,
+                   int num_seqs, int row_stride);
+/* prefix_attn/prefix_tree.py:146-149  build_radix_tree(seq_lens, list of unpadded lists):
+ * row i is flat_pages[offsets[i] .. offsets[i+1]). */
+int pat_tree_build_ragged(pat_tree* t, const int32_t* seq_lens, const int32_t* flat_pages,
+                          const int64_t* offsets, int num_seqs);
+
+/* csrc/bindings.cpp:128-144 / csrc/prefix_tree.h:183-324 / prefix_tree.py:548-616
+ * pack_schedule(MNWs, HRatio, kvHead, use_compute_model).  mnws = num_mnws x 3 ints or NULL/0
+ * for the 11 default tile shapes. */
+int pat_tree_pack(pat_tree* t, const int32_t* mnws, int num_mnws, int hratio, int kv_heads,
+                  int use_compute_model);
+
+/* Plan accessors (struct KernelInfo, csrc/prefix_tree.h:7-25).  Pointers stay valid until the
+ * next pack / destroy. */
+typedef struct pat_bucket_view {
+    int32_t mnw[3];
+    int32_t ctas;
+    int32_t max_seqs;            /* row width of q_table */
+    int32_t max_blocks;          /* row width of block_table */
+    const int32_t* q_table;      /* [ctas, max_seqs]  zero padded */
+    const int32_t* block_table;  /* [ctas, max_blocks] zero padded */
+    const int32_t* num_seqs;     /* [ctas] */
+    const int32_t* cta_ranks;    /* [ctas] */
+    const int32_t* kv_in_cta;    /* [ctas] */
+} pat_bucket_view;
+
+int pat_tree_num_buckets(const pat_tree* t);
+int pat_tree_bucket(const pat_tree* t, int index, pat_bucket_view* out);
+/* num_split_per_seq [batch]; *batch receives the length */
+const int32_t* pat_tree_split_per_seq(const pat_tree* t, int* batch);
+/* out[0..2] = max_split_per_seq, max_seqs_in_CTA, max_blocks_in_CTA */
+int pat_tree_maxima(const pat_tree* t, int32_t out[3]);
+
+/* Tree inspection (the Python class exposes the same arrays, prefix_tree.py:50-58). */
+int pat_tree_num_nodes(const pat_tree* t);
+/* out[0..3] = parent, s_value, length, number of pages on the edge */
+int pat_tree_node(const pat_tree* t, int node, int32_t out[4]);
+int pat_tree_node_seqs(const pat_tree* t, int node, const int32_t** seqs, int* count);
+int pat_tree_node_pages(const pat_tree* t, int node, const int32_t** pages, int* count);
+/* children in the order the packer visits them; returns the count (<= cap are written) */
+int pat_tree_node_children(const pat_tree* t, int node, int32_t* out, int cap);
+
+/* ------------------------------------------------------------------------- *
+ * Work list: reference-format plan -> device work items (host).
+ * No counterpart as a function in the reference: there a box IS the CTA
+ * (csrc/pat_fwd_launch_template.h:35-50, csrc/block_info.h:14-39).
+ * ------------------------------------------------------------------------- */
+typedef struct pat_work pat_work;
+
+typedef struct pat_plan_bucket {
+    int32_t ctas;
+    int32_t q_stride;
+    int32_t block_stride;
+    int32_t reserved;
+    const int32_t* q_table;
+    const int32_t* block_table;
+    const int32_t* num_seqs;
+    const int32_t* kv_in_cta;
+} pat_plan_bucket;
+
+typedef struct pat_work_options {
+    int32_t num_sms;             /* 0 = 148 */
+    int32_t dense_min_rows;      /* segments with >= this many query rows use the dense kernel; 0 = default */
+    int32_t chunk_tokens_min;    /* 0 = default */
+    int32_t chunk_tokens_max;    /* 0 = default */
+    int32_t dense_chunk_tokens_max; /* 0 = default */
+    int32_t items_per_sm;        /* 0 = default */
+    int32_t disable_dense;       /* 1 = every segment goes through the streaming kernel */
+    int32_t reserved;
+} pat_work_options;
+
+typedef struct pat_work_header {
+    int32_t batch, hratio, page_size;
+    int32_t num_stream_items, num_dense_items, num_entries, max_entries_per_query;
+    int32_t items_off, queries_off, pages_off, merge_indptr_off, merge_entries_off;
+    int32_t blob_words, num_segments;
+    int32_t max_page_id, reserved;
+    int64_t unique_tokens, stream_tokens, dense_tokens;
+} pat_work_header;
+
+/* Returns NULL and sets *status on failure. num_cache_pages > 0 enables a range check of page ids. */
+pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int batch, int hratio,
+                          int kv_heads, int page_size, int64_t num_cache_pages,
+                          const pat_work_options* options, int* status);
+/* Same, straight from a packed tree. */
+pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_t num_cache_pages,
+                             const pat_work_options* options, int* status);
+void pat_work_destroy(pat_work* w);
+int pat_work_get_header(const pat_work* w, pat_work_header* out);
+/* int32 blob to copy to the device as is; *words receives its length */
+const int32_t* pat_work_blob(const pat_work* w, size_t* words);
+
+/* ------------------------------------------------------------------------- *
+ * Decode attention on the device.
+ * Replaces pat::pat_mha_fwd_kvcache (csrc/api.h:110-295) and the launcher
+ * pat_run_mha_fwd_splitkv_dispatch (csrc/pat_fwd_launch_template.h:52-98).
+ * ------------------------------------------------------------------------- */
+enum { PAT_DTYPE_FP16 = 0, PAT_DTYPE_BF16 = 1 };
+
+typedef struct pat_decode_args {
+    /* tensors (device pointers), strides in elements, last dimension contiguous */
+    const void* q;        /* [batch, 1, num_q_heads, head_dim] */
+    const void* k_cache;  /* [num_pages, page_size, num_kv_heads, head_dim] */
+    const void* v_cache;
+    void* out;            /* [batch, 1, num_q_heads, head_dim], same dtype as q */
+    float* lse_out;       /* optional [batch, num_q_heads]: natural-log LSE of the scaled scores */
+    int64_t q_batch_stride, q_head_stride;
+    int64_t k_page_stride, k_row_stride, k_head_stride;
+    int64_t v_page_stride, v_row_stride, v_head_stride;
+    int64_t out_batch_stride, out_head_stride;
+    int32_t batch, num_q_heads, num_kv_heads, head_dim;
+    int32_t page_size;
+    int32_t dtype;        /* PAT_DTYPE_* */
+    int64_t num_pages;
+    float softmax_scale;
+    int32_t flags;        /* reserved, 0 */
+    /* work list */
+    const int32_t* work_blob;   /* device copy of pat_work_blob */
+    pat_work_header work;       /* host copy of the header */
+    /* scratch for the per-(item, query) partial results */
+    void* workspace;
+    size_t workspace_bytes;
+    /* optional device int32[4]: [0] != 0 after the call means a bounded wait gave up */
+    int32_t* status_word;
+} pat_decode_args;
+
+size_t pat_b200_workspace_bytes(const pat_work_header* work, int num_q_heads, int head_dim);
+/* Enqueues the kernels on `stream` (a cudaStream_t) of the current device and returns. */
+int pat_b200_decode(const pat_decode_args* args, void* stream);
+/* Number of kernels the last successful pat_b200_decode call on this thread launched. */
+int pat_b200_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAT_B200_H_ */

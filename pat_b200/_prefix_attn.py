@@ -1,0 +1,481 @@
+"""The op and the native scheduler objects, bound over the C ABI.
+
+Python-facing equivalent of the reference's compiled module
+``prefix_attn._prefix_attn`` (``csrc/bindings.cpp:74-158``, stub
+``prefix_attn/_prefix_attn.pyi``): the two forms of
+``prefix_attn_with_kvcache``, ``PrefixTreeCPP`` and its ``KernelInfo``.  All
+device work goes through ``libpat_b200.so``; nothing here computes attention.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from . import _native as N
+from . import _plan_cache
+
+__all__ = ["prefix_attn_with_kvcache", "PrefixTreeCPP", "KernelInfo", "WorkConfig", "DeviceWork"]
+
+
+# --------------------------------------------------------------------------- options
+class WorkConfig:
+    """Tuning knobs of the work-list builder (0 = library default)."""
+
+    __slots__ = ("num_sms", "dense_min_rows", "chunk_tokens_min", "chunk_tokens_max",
+                 "dense_chunk_tokens_max", "items_per_sm", "disable_dense")
+
+    def __init__(self, **kw):
+        for name in self.__slots__:
+            setattr(self, name, int(kw.pop(name, 0)))
+        if kw:
+            raise TypeError(f"unknown work options: {sorted(kw)}")
+
+    def key(self):
+        return tuple(getattr(self, n) for n in self.__slots__)
+
+    def as_struct(self) -> N.WorkOptions:
+        s = N.WorkOptions()
+        for name in self.__slots__:
+            setattr(s, name, getattr(self, name))
+        return s
+
+
+def _env_config() -> WorkConfig:
+    """Defaults, overridable through ``PAT_B200_<OPTION>`` environment variables."""
+    kw = {}
+    for name in WorkConfig.__slots__:
+        v = os.environ.get("PAT_B200_" + name.upper())
+        if v:
+            kw[name] = int(v)
+    return WorkConfig(**kw)
+
+
+_default_config: Optional[WorkConfig] = None
+
+
+def default_config() -> WorkConfig:
+    global _default_config
+    if _default_config is None:
+        _default_config = _env_config()
+    return _default_config
+
+
+def set_default_config(cfg: Optional[WorkConfig]) -> None:
+    global _default_config
+    _default_config = cfg
+
+
+def _sm_count(device: torch.device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+# --------------------------------------------------------------------------- device work list
+class DeviceWork:
+    """A work list on one device: the int32 blob plus the host header."""
+
+    def __init__(self, handle: int, device: torch.device):
+        lib = N.load()
+        self.header = N.WorkHeader()
+        lib.pat_work_get_header(handle, C.byref(self.header))
+        words = C.c_size_t()
+        ptr = lib.pat_work_blob(handle, C.byref(words))
+        host = torch.from_numpy(np.ctypeslib.as_array(ptr, shape=(words.value,)).copy())
+        if device.type == "cuda":
+            host = host.pin_memory()
+        self._host = host                       # kept alive until the async copy is done
+        self.blob = host.to(device, non_blocking=True)
+        self.device = device
+        lib.pat_work_destroy(handle)
+
+    @classmethod
+    def from_host_plan(cls, plan: "_plan_cache.HostPlan", hratio: int, kv_heads: int, page_size: int,
+                       device: torch.device, cfg: WorkConfig) -> "DeviceWork":
+        lib = N.load()
+        n = len(plan.q_tables)
+        buckets = (N.PlanBucket * max(n, 1))()
+        for i in range(n):
+            q, b = plan.q_tables[i], plan.block_tables[i]
+            buckets[i].ctas = int(plan.num_seqs[i].shape[0])
+            buckets[i].q_stride = int(q.shape[1])
+            buckets[i].block_stride = int(b.shape[1])
+            buckets[i].q_table = q.ctypes.data
+            buckets[i].block_table = b.ctypes.data
+            buckets[i].num_seqs = plan.num_seqs[i].ctypes.data
+            buckets[i].kv_in_cta = plan.kv_lens[i].ctypes.data
+        opts = cfg.as_struct()
+        if opts.num_sms == 0 and device.type == "cuda":
+            opts.num_sms = _sm_count(device)
+        status = C.c_int(0)
+        handle = lib.pat_work_create(buckets, n, plan.batch, hratio, kv_heads, page_size, 0,
+                                     C.byref(opts), C.byref(status))
+        if not handle:
+            raise RuntimeError(f"invalid plan: {N.strerror(status.value)}")
+        return cls(handle, device)
+
+    @classmethod
+    def from_tree(cls, tree_handle: int, hratio: int, kv_heads: int, device: torch.device,
+                  cfg: WorkConfig) -> "DeviceWork":
+        lib = N.load()
+        opts = cfg.as_struct()
+        if opts.num_sms == 0 and device.type == "cuda":
+            opts.num_sms = _sm_count(device)
+        status = C.c_int(0)
+        handle = lib.pat_work_from_tree(tree_handle, hratio, kv_heads, 0, C.byref(opts), C.byref(status))
+        if not handle:
+            raise RuntimeError(f"invalid plan: {N.strerror(status.value)}")
+        return cls(handle, device)
+
+
+# --------------------------------------------------------------------------- native scheduler
+def _view_i32(ptr, shape) -> torch.Tensor:
+    """A CPU int32 tensor holding a copy of native memory."""
+    n = int(np.prod(shape)) if len(shape) else 1
+    if n == 0:
+        return torch.zeros(shape, dtype=torch.int32)
+    return torch.from_numpy(np.ctypeslib.as_array(ptr, shape=(n,)).reshape(shape).copy())
+
+
+class KernelInfo:
+    """Plan produced by ``PrefixTreeCPP.pack_schedule`` (reference
+    ``csrc/prefix_tree.h:7-39``): per-bucket int32 CPU tensors until
+    ``to_gpu(device)`` moves them - and builds and uploads the device work
+    list the kernels consume."""
+
+    def __init__(self, owner: "PrefixTreeCPP"):
+        self._owner = owner
+        self.q_tables: List[torch.Tensor] = []
+        self.block_tables: List[torch.Tensor] = []
+        self.num_seqs_per_CTAs: List[torch.Tensor] = []
+        self.CTA_ranks: List[torch.Tensor] = []
+        self.kv_in_CTAs: List[torch.Tensor] = []
+        self.MNWs: List[List[int]] = []
+        self.num_split_per_seq: torch.Tensor = torch.zeros(0, dtype=torch.int32)
+        self.max_split_per_seq = 0
+        self.max_seqs_in_CTA = 0
+        self.max_blocks_in_CTA = 0
+        self._work = {}
+
+    def _refresh(self):
+        lib = N.load()
+        h = self._owner._handle
+        self.q_tables, self.block_tables, self.num_seqs_per_CTAs = [], [], []
+        self.CTA_ranks, self.kv_in_CTAs, self.MNWs = [], [], []
+        view = N.BucketView()
+        for i in range(lib.pat_tree_num_buckets(h)):
+            lib.pat_tree_bucket(h, i, C.byref(view))
+            self.MNWs.append([view.mnw[0], view.mnw[1], view.mnw[2]])
+            self.q_tables.append(_view_i32(view.q_table, (view.ctas, view.max_seqs)))
+            self.block_tables.append(_view_i32(view.block_table, (view.ctas, view.max_blocks)))
+            self.num_seqs_per_CTAs.append(_view_i32(view.num_seqs, (view.ctas,)))
+            self.CTA_ranks.append(_view_i32(view.cta_ranks, (view.ctas,)))
+            self.kv_in_CTAs.append(_view_i32(view.kv_in_cta, (view.ctas,)))
+        n = C.c_int(0)
+        ptr = lib.pat_tree_split_per_seq(h, C.byref(n))
+        self.num_split_per_seq = _view_i32(ptr, (n.value,))
+        mx = (C.c_int32 * 3)()
+        lib.pat_tree_maxima(h, mx)
+        self.max_split_per_seq, self.max_seqs_in_CTA, self.max_blocks_in_CTA = mx[0], mx[1], mx[2]
+        self._work = {}
+
+    def to_gpu(self, device: Union[torch.device, str]) -> None:
+        device = torch.device(device)
+        if device.type == "cuda" and device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        move = lambda t: t.to(device, non_blocking=True)
+        self.q_tables = [move(t) for t in self.q_tables]
+        self.block_tables = [move(t) for t in self.block_tables]
+        self.num_seqs_per_CTAs = [move(t) for t in self.num_seqs_per_CTAs]
+        self.CTA_ranks = [move(t) for t in self.CTA_ranks]
+        self.kv_in_CTAs = [move(t) for t in self.kv_in_CTAs]
+        self.num_split_per_seq = move(self.num_split_per_seq)
+        if device.type == "cuda":
+            self.device_work(device)
+
+    def device_work(self, device: torch.device, cfg: Optional[WorkConfig] = None) -> DeviceWork:
+        cfg = cfg or default_config()
+        key = (str(device), cfg.key())
+        work = self._work.get(key)
+        if work is None:
+            o = self._owner
+            work = DeviceWork.from_tree(o._handle, o._hratio, o._kv_heads, device, cfg)
+            self._work[key] = work
+        return work
+
+
+class PrefixTreeCPP:
+    """Native radix tree + packer (reference ``csrc/bindings.cpp:100-146``).
+
+    ``semantics="cpp"`` (default) follows ``csrc/prefix_tree.h``;
+    ``semantics="py"`` follows ``prefix_attn/prefix_tree.py`` bit for bit (the
+    two reference schedulers differ in thresholds and visiting order).
+    """
+
+    def __init__(self, block_size: int, semantics: str = "cpp"):
+        if semantics not in ("cpp", "py"):
+            raise ValueError("semantics must be 'cpp' or 'py'")
+        lib = N.load()
+        self.block_size = int(block_size)
+        self.semantics = semantics
+        self._handle = lib.pat_tree_create(self.block_size, 1 if semantics == "cpp" else 0)
+        if not self._handle:
+            raise RuntimeError("block_size must be positive")
+        self._kernel_info = KernelInfo(self)
+        self._hratio = 1
+        self._kv_heads = 8
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h:
+            try:
+                N.load().pat_tree_destroy(h)
+            except Exception:
+                pass
+            self._handle = None
+
+    @property
+    def kernel_info(self) -> KernelInfo:
+        return self._kernel_info
+
+    def build_radix_tree(self, seq_lens, block_table) -> None:
+        """``seq_lens``: list of ints or a CPU int32 tensor; ``block_table``: a
+        CPU int32 tensor ``[num_seqs, max_blocks]`` (rows are cut to
+        ``ceil(len / block_size)`` pages) or, as the Python scheduler takes
+        it, a list of unpadded lists."""
+        lib = N.load()
+        if isinstance(seq_lens, torch.Tensor):
+            if seq_lens.dtype != torch.int32 or seq_lens.device.type != "cpu":
+                raise RuntimeError("seq_lens must be a List[int] or a CPU Int32 Tensor")
+            lens = np.ascontiguousarray(seq_lens.numpy())
+        elif isinstance(seq_lens, (list, tuple)):
+            lens = np.asarray(seq_lens, dtype=np.int32)
+        else:
+            raise RuntimeError("seq_lens must be a List[int] or a CPU Int32 Tensor")
+        if isinstance(block_table, torch.Tensor):
+            if block_table.dtype != torch.int32 or block_table.device.type != "cpu" or block_table.dim() != 2:
+                raise RuntimeError("block_table must be a 2-D CPU Int32 Tensor")
+            table = np.ascontiguousarray(block_table.numpy())
+            if lens.shape[0] != table.shape[0]:
+                raise RuntimeError("Seq lens list mismatch")
+            rc = lib.pat_tree_build(self._handle, lens.ctypes.data, table.ctypes.data,
+                                    table.shape[0], table.shape[1])
+        else:
+            rows = [np.asarray(r, dtype=np.int32) for r in block_table]
+            if lens.shape[0] != len(rows):
+                raise RuntimeError("Seq lens list mismatch")
+            offsets = np.zeros(len(rows) + 1, dtype=np.int64)
+            np.cumsum([len(r) for r in rows], out=offsets[1:])
+            flat = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int32)
+            flat = np.ascontiguousarray(flat, dtype=np.int32)
+            rc = lib.pat_tree_build_ragged(self._handle, lens.ctypes.data, flat.ctypes.data,
+                                           offsets.ctypes.data, len(rows))
+        if rc != 0:
+            raise RuntimeError(f"build_radix_tree failed: {N.strerror(rc)}")
+
+    def pack_schedule(self, MNWs: Optional[List[List[int]]] = None, HRatio: int = 1, kvHead: int = 8,
+                      use_compute_model: bool = False) -> None:
+        lib = N.load()
+        if MNWs:
+            arr = np.asarray(MNWs, dtype=np.int32).reshape(-1, 3)
+            ptr, n = arr.ctypes.data, arr.shape[0]
+        else:
+            arr, ptr, n = None, None, 0
+        rc = lib.pat_tree_pack(self._handle, ptr, n, int(HRatio), int(kvHead), int(bool(use_compute_model)))
+        if rc == -2:
+            raise IndexError(N.strerror(rc))
+        if rc == -3:
+            raise ValueError(N.strerror(rc))
+        if rc == -4:
+            raise KeyError(N.strerror(rc))
+        if rc != 0:
+            raise RuntimeError(f"pack_schedule failed: {N.strerror(rc)}")
+        self._hratio, self._kv_heads = int(HRatio), int(kvHead)
+        self._kernel_info._refresh()
+
+    # ---- inspection helpers (not in the reference binding) -----------------
+    def nodes(self):
+        """``[(parent, s_value, length, seq_indices, pages, children)]`` per node."""
+        lib = N.load()
+        out = []
+        info = (C.c_int32 * 4)()
+        ptr, cnt = N.i32p(), C.c_int(0)
+        for i in range(lib.pat_tree_num_nodes(self._handle)):
+            lib.pat_tree_node(self._handle, i, info)
+            lib.pat_tree_node_seqs(self._handle, i, C.byref(ptr), C.byref(cnt))
+            seqs = [ptr[j] for j in range(cnt.value)]
+            lib.pat_tree_node_pages(self._handle, i, C.byref(ptr), C.byref(cnt))
+            pages = [ptr[j] for j in range(cnt.value)]
+            nkids = lib.pat_tree_node_children(self._handle, i, None, 0)
+            buf = (C.c_int32 * max(nkids, 1))()
+            lib.pat_tree_node_children(self._handle, i, buf, nkids)
+            out.append((info[0], info[1], info[2], seqs, pages, [buf[j] for j in range(nkids)]))
+        return out
+
+
+# --------------------------------------------------------------------------- the op
+_DTYPES = {torch.float16: 0, torch.bfloat16: 1}
+
+
+def _check(cond: bool, msg: str):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_index(t: torch.Tensor, name: str, shape=None):
+    _check(t.is_cuda, f"{name} must be on CUDA")
+    _check(t.dtype == torch.int32, f"{name} must have dtype torch.int32")
+    _check(t.stride(-1) == 1 or t.shape[-1] <= 1, f"{name} must have contiguous last dimension")
+    if shape is not None:
+        _check(tuple(t.shape) == tuple(shape), f"{name} must have shape {tuple(shape)}")
+
+
+def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None, status=None):
+    lib = N.load()
+    B, _, H, D = q.shape
+    a = N.DecodeArgs()
+    a.q, a.k_cache, a.v_cache, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+    a.lse_out = lse_out.data_ptr() if lse_out is not None else None
+    a.q_batch_stride, a.q_head_stride = q.stride(0), q.stride(2)
+    a.k_page_stride, a.k_row_stride, a.k_head_stride = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+    a.v_page_stride, a.v_row_stride, a.v_head_stride = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
+    a.out_batch_stride, a.out_head_stride = out.stride(0), out.stride(2)
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = B, H, k_cache.shape[2], D
+    a.page_size = k_cache.shape[1]
+    a.dtype = _DTYPES[q.dtype]
+    a.num_pages = k_cache.shape[0]
+    a.softmax_scale = float(scale)
+    a.work_blob = work.blob.data_ptr()
+    a.work = work.header
+    need = lib.pat_b200_workspace_bytes(C.byref(work.header), H, D)
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need
+    a.status_word = status.data_ptr() if status is not None else None
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    rc = lib.pat_b200_decode(C.byref(a), C.c_void_p(stream))
+    if rc != 0:
+        raise RuntimeError(f"prefix_attn_with_kvcache failed: {N.strerror(rc)} ({rc})")
+
+
+def prefix_attn_with_kvcache(*args, **kwargs) -> None:
+    """Prefix-aware decode attention over a paged KV cache; writes ``out`` in place.
+
+    Two call forms, as in the reference (``csrc/bindings.cpp:76-95`` and ``:148-157``):
+
+    ``(q, k_cache_paged, v_cache_paged, num_split_per_seq, query_tables, block_tables,
+    num_seqs_per_CTAs, CTA_ranks, kv_in_CTAs, MNW, max_split_per_seq, max_seqs_in_CTA,
+    max_blocks_in_CTA, softmax_scale, out, timing_=None)``
+
+    ``(q, k_cache_paged, v_cache_paged, tree, softmax_scale, out)`` with ``tree`` a
+    ``PrefixTreeCPP`` whose ``kernel_info`` was moved to the GPU.
+
+    ``q``/``out``: ``[batch, 1, heads, head_dim]``; caches: ``[pages, page_size, kv_heads,
+    head_dim]``; fp16 or bf16.  Extra keyword (not in the reference): ``lse_out``, a float32
+    CUDA tensor ``[batch, heads]`` that receives the natural-log LSE of the scaled scores
+    (the reference computes it, ``csrc/api.h:195``, but never returns it).
+    """
+    lse_out = kwargs.pop("lse_out", None)
+    status = kwargs.pop("_status", None)
+    names16 = ["q", "k_cache_paged", "v_cache_paged", "num_split_per_seq", "query_tables", "block_tables",
+               "num_seqs_per_CTAs", "CTA_ranks", "kv_in_CTAs", "MNW", "max_split_per_seq", "max_seqs_in_CTA",
+               "max_blocks_in_CTA", "softmax_scale", "out", "timing_"]
+    names6 = ["q", "k_cache_paged", "v_cache_paged", "tree", "softmax_scale", "out", "timing_"]
+    tree_form = ("tree" in kwargs) or (len(args) >= 4 and isinstance(args[3], PrefixTreeCPP))
+    names = names6 if tree_form else names16
+    if len(args) > len(names):
+        raise TypeError("prefix_attn_with_kvcache(): incompatible function arguments")
+    bound = dict(zip(names, args))
+    for k, v in kwargs.items():
+        if k not in names or k in bound:
+            raise TypeError(f"prefix_attn_with_kvcache(): incompatible function arguments ({k})")
+        bound[k] = v
+    bound.setdefault("timing_", None)
+    missing = [n for n in names if n not in bound]
+    if missing:
+        raise TypeError(f"prefix_attn_with_kvcache(): missing arguments {missing}")
+
+    q, k_cache, v_cache, out = bound["q"], bound["k_cache_paged"], bound["v_cache_paged"], bound["out"]
+    scale = bound["softmax_scale"]
+
+    # ---- the reference's argument checks (csrc/api.h:131-181) ----------------
+    _check(q.dtype in _DTYPES, "only support fp16 and bf16 data type")
+    _check(k_cache.dtype == q.dtype, "query and key must have the same dtype")
+    _check(v_cache.dtype == q.dtype, "query and value must have the same dtype")
+    for t, n in ((q, "q"), (k_cache, "kcache"), (v_cache, "vcache")):
+        _check(t.is_cuda, f"{n} must be on CUDA")
+    for t in (q, k_cache, v_cache):
+        _check(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+    _check(q.dim() == 4 and k_cache.dim() == 4 and v_cache.dim() == 4, "q, kcache, vcache must be 4-D")
+    B, seqlen_q, H, D = q.shape
+    if D not in (64, 128):
+        raise RuntimeError("head_size_og must be 64 / 128 currently")
+    num_pages, page, Hkv = k_cache.shape[0], k_cache.shape[1], k_cache.shape[2]
+    _check(page % 16 == 0, "Paged KV cache block size must be divisible by 16")
+    _check(H % Hkv == 0, "Number of heads in key/value must divide number of heads in query")
+    ratio = H // Hkv
+    _check(ratio in (1, 2, 4, 8), "only support QGA with hq/hkv = 1, 2, 4, 8 now.")
+    _check(B > 0, "batch size must be positive")
+    _check(seqlen_q == 1, "q must have shape (batch_size, 1, n_heads, head_size)")
+    _check(tuple(k_cache.shape) == (num_pages, page, Hkv, D), "kcache must have shape (num_blocks, page_block_size, n_heads_kv, head_size_og)")
+    _check(tuple(v_cache.shape) == (num_pages, page, Hkv, D), "vcache must have shape (num_blocks, page_block_size, n_heads_kv, head_size_og)")
+    _check(out.is_cuda and out.dtype == q.dtype and tuple(out.shape) == tuple(q.shape) and out.stride(-1) == 1,
+           "out must be a CUDA tensor with the shape and dtype of q")
+    if lse_out is not None:
+        _check(lse_out.is_cuda and lse_out.dtype == torch.float32 and lse_out.is_contiguous()
+               and tuple(lse_out.shape) == (B, H), "lse_out must be a contiguous float32 CUDA tensor [batch, heads]")
+
+    if tree_form:
+        tree = bound["tree"]
+        inner = getattr(tree, "tree", None)         # an AsyncTree hands over its built tree
+        if not isinstance(tree, PrefixTreeCPP) and isinstance(inner, PrefixTreeCPP):
+            tree = inner
+        _check(isinstance(tree, PrefixTreeCPP), "tree must be a PrefixTreeCPP")
+        info = tree.kernel_info
+        max_split = info.max_split_per_seq
+        nsplit = info.num_split_per_seq
+    else:
+        max_split = int(bound["max_split_per_seq"])
+        nsplit = bound["num_split_per_seq"]
+    if max_split > 32:
+        raise RuntimeError("Currently, only supports up to 32 splits per seq. Excessive splitting may reduce efficiency.")
+    if max_split <= 0:
+        raise RuntimeError("there is no case that a seq has no block")
+    _check_index(nsplit, "num_split_per_seq", (B,))
+
+    if tree_form:
+        _check(tree._hratio == ratio, "the plan was packed for a different HRatio than q / k_cache imply")
+        _check(tree.block_size == page, "the plan was built for a different page size than k_cache has")
+        work = info.device_work(q.device)
+    else:
+        qts, bts = list(bound["query_tables"]), list(bound["block_tables"])
+        nss, rks, kvs = list(bound["num_seqs_per_CTAs"]), list(bound["CTA_ranks"]), list(bound["kv_in_CTAs"])
+        mnw = bound["MNW"]
+        _check(len(qts) == len(bts) == len(nss) == len(rks) == len(kvs) == len(mnw),
+               "per-bucket plan lists must have one entry per MNW")
+        for i in range(len(mnw)):
+            ctas = qts[i].shape[0]
+            _check_index(qts[i], "query_tables")
+            _check_index(bts[i], "block_tables")
+            _check(bts[i].shape[0] == ctas, "block_tables must have one row per CTA")
+            _check_index(nss[i], "num_seqs_per_CTA", (ctas,))
+            _check_index(rks[i], "CTA_rank", (ctas,))
+            _check_index(kvs[i], "kv_in_CTA", (ctas,))
+        tag = _plan_cache.find_tag(nsplit, qts, bts, nss, kvs)
+        if tag is None:
+            tag = _plan_cache.make_tag(nsplit, qts, bts, nss, kvs)
+        cfg = default_config()
+        key = (str(q.device), ratio, Hkv, page, cfg.key())
+        work = tag.work.get(key)
+        if work is None:
+            work = DeviceWork.from_host_plan(tag.host_plan, ratio, Hkv, page, q.device, cfg)
+            tag.work[key] = work
+
+    with torch.cuda.device(q.device):
+        _run(q, k_cache, v_cache, work, scale, out, lse_out, status)
+
+
+def last_launch_count() -> int:
+    """Kernels launched by the last call on this thread."""
+    return N.load().pat_b200_last_launch_count()

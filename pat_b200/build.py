@@ -1,0 +1,64 @@
+"""Builds ``libpat_b200.so`` (C-ABI library: scheduler, work-list builder, sm_100a
+kernels and their launcher) in-tree with nvcc.
+
+    python -m pat_b200.build [--force] [--verbose]
+
+nvcc cross-compiles for sm_100a without a GPU.  The library links the CUDA
+runtime statically and resolves the one driver symbol it needs
+(``cuTensorMapEncodeTiled``) at run time, so it loads on a machine without a
+GPU driver as well.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB_PATH = os.path.join(HERE, "libpat_b200.so")
+SOURCES = ["pat_tree.cpp", "pat_work.cpp", "pat_capi.cpp", "pat_decode.cu"]
+HEADERS = ["pat_tree.h", "pat_work.h", "pat_device.cuh", "pat_kernels.cuh",
+           os.path.join("..", "..", "include", "pat_b200.h")]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or add it to PATH")
+
+
+def needs_build() -> bool:
+    if not os.path.isfile(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    return any(os.path.getmtime(d) > built for d in deps if os.path.isfile(d))
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not needs_build():
+        return LIB_PATH
+    cmd = [
+        _nvcc(), "-shared", "-Xcompiler", "-fPIC", "-std=c++17", "-O3", "-lineinfo",
+        "-gencode", "arch=compute_100a,code=sm_100a",
+        "-x", "cu",
+        "-o", LIB_PATH,
+    ] + [os.path.join(CSRC, s) for s in SOURCES]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print(res.stdout, res.stderr, sep="\n")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

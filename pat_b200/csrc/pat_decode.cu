@@ -1,0 +1,204 @@
+// Host launcher of the decode-attention kernels (C ABI: pat_b200_decode).
+//
+// Replaces pat::pat_mha_fwd_kvcache (csrc/api.h:110-295: argument checks,
+// scratch set-up, one parameter block per tile bucket) and
+// pat_run_mha_fwd_splitkv_dispatch (csrc/pat_fwd_launch_template.h:52-98: one
+// stream per bucket, gather on the legacy stream).  Here everything runs on the
+// caller's stream: streaming items, dense items, then the merge.
+#include "../../include/pat_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+
+#include "pat_kernels.cuh"
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeFn>(sym);
+    }();
+    return fn;
+}
+
+// View of a paged cache [pages, page_size, kv_heads, D] as a 4-D tensor
+// (D, kv_heads, page_size, pages) with a [64, 1, 16, 1] box and 128-byte swizzle.
+int make_cache_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int head_dim, int kv_heads,
+                   int page_size, int64_t pages, int64_t head_stride, int64_t row_stride, int64_t page_stride) {
+    EncodeFn enc = get_encode_fn();
+    if (!enc) return PAT_ERR_CUDA;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(kv_heads),
+                                static_cast<cuuint64_t>(page_size), static_cast<cuuint64_t>(pages)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_stride) * 2, static_cast<cuuint64_t>(row_stride) * 2,
+                                   static_cast<cuuint64_t>(page_stride) * 2};
+    const cuuint32_t box[4] = {64, 1, 16, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult rc = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? PAT_OK : PAT_ERR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+thread_local int g_last_launches = 0;
+constexpr int kMaxDevices = 64;
+
+template <typename T, int D>
+int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
+    using namespace pat;
+    CUtensorMap kmap, vmap;
+    int rc = make_cache_map(&kmap, a.k_cache, Elt<T>::kTma, D, a.num_kv_heads, a.page_size, a.num_pages,
+                            a.k_head_stride, a.k_row_stride, a.k_page_stride);
+    if (rc != PAT_OK) return rc;
+    rc = make_cache_map(&vmap, a.v_cache, Elt<T>::kTma, D, a.num_kv_heads, a.page_size, a.num_pages,
+                        a.v_head_stride, a.v_row_stride, a.v_page_stride);
+    if (rc != PAT_OK) return rc;
+
+    const size_t rows = static_cast<size_t>(a.work.num_entries) * a.num_q_heads;
+    float* part_o = static_cast<float*>(a.workspace);
+    float* part_lse = part_o + rows * D;
+
+    AttnParams p{};
+    p.q = a.q;
+    p.part_o = part_o;
+    p.part_lse = part_lse;
+    p.queries = a.work_blob + a.work.queries_off;
+    p.pages = a.work_blob + a.work.pages_off;
+    p.q_batch_stride = a.q_batch_stride;
+    p.q_head_stride = a.q_head_stride;
+    p.kv_heads = a.num_kv_heads;
+    p.hratio = a.work.hratio;
+    p.num_q_heads = a.num_q_heads;
+    p.page_size = a.page_size;
+    p.scale = a.softmax_scale;
+    p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+    p.status = a.status_word;
+
+    int launches = 0;
+    if (a.work.num_stream_items > 0) {
+        static bool configured[kMaxDevices] = {};
+        auto kern = stream_kernel<T, D>;
+        constexpr int smem = stream_smem_bytes<D>();
+        if (!configured[dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return PAT_ERR_CUDA;
+            configured[dev] = true;
+        }
+        p.items = a.work_blob + a.work.items_off;
+        p.num_items = a.work.num_stream_items;
+        const long long grid = static_cast<long long>(p.num_items) * a.num_kv_heads;
+        if (grid > 0x7fffffffLL) return PAT_ERR_TOO_LARGE;
+        kern<<<static_cast<unsigned>(grid), kStreamWarps * 32, smem, stream>>>(p, kmap, vmap);
+        ++launches;
+    }
+    if (a.work.num_dense_items > 0) {
+        static bool configured[kMaxDevices] = {};
+        auto kern = dense_kernel<T, D>;
+        constexpr int smem = dense_smem_bytes<D>();
+        if (!configured[dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return PAT_ERR_CUDA;
+            configured[dev] = true;
+        }
+        p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
+        p.num_items = a.work.num_dense_items;
+        const long long grid = static_cast<long long>(p.num_items) * a.num_kv_heads;
+        if (grid > 0x7fffffffLL) return PAT_ERR_TOO_LARGE;
+        kern<<<static_cast<unsigned>(grid), (kDenseWarps + 1) * 32, smem, stream>>>(p, kmap, vmap);
+        ++launches;
+    }
+    {
+        MergeParams mp{};
+        mp.part_o = part_o;
+        mp.part_lse = part_lse;
+        mp.indptr = a.work_blob + a.work.merge_indptr_off;
+        mp.entries = a.work_blob + a.work.merge_entries_off;
+        mp.out = a.out;
+        mp.lse_out = a.lse_out;
+        mp.out_batch_stride = a.out_batch_stride;
+        mp.out_head_stride = a.out_head_stride;
+        mp.batch = a.batch;
+        mp.num_q_heads = a.num_q_heads;
+        const int total = a.batch * a.num_q_heads;
+        const int warps_per_cta = 8;
+        merge_kernel<T, D><<<(total + warps_per_cta - 1) / warps_per_cta, warps_per_cta * 32, 0, stream>>>(mp);
+        ++launches;
+    }
+    if (cudaGetLastError() != cudaSuccess) return PAT_ERR_CUDA;
+    g_last_launches = launches;
+    return PAT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t pat_b200_workspace_bytes(const pat_work_header* work, int num_q_heads, int head_dim) {
+    if (!work || num_q_heads <= 0 || head_dim <= 0) return 0;
+    const size_t rows = static_cast<size_t>(work->num_entries) * num_q_heads;
+    // partial outputs + partial LSEs, rounded up to 256 B
+    const size_t bytes = rows * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
+    return (bytes + 255) / 256 * 256 + 256;
+}
+
+int pat_b200_last_launch_count(void) { return g_last_launches; }
+
+int pat_b200_decode(const pat_decode_args* args, void* stream_handle) {
+    if (!args) return PAT_ERR_BAD_ARGUMENT;
+    const pat_decode_args& a = *args;
+    if (!a.q || !a.k_cache || !a.v_cache || !a.out || !a.work_blob) return PAT_ERR_BAD_ARGUMENT;
+    if (a.batch <= 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0 || a.num_pages <= 0) return PAT_ERR_BAD_ARGUMENT;
+    if (a.num_q_heads % a.num_kv_heads != 0) return PAT_ERR_BAD_ARGUMENT;
+    if (a.work.batch != a.batch || a.work.hratio != a.num_q_heads / a.num_kv_heads ||
+        a.work.page_size != a.page_size)
+        return PAT_ERR_BAD_PLAN;
+    if (a.work.max_page_id >= a.num_pages) return PAT_ERR_BAD_PLAN;
+    if (a.head_dim != 64 && a.head_dim != 128) return PAT_ERR_UNSUPPORTED;
+    if (a.dtype != PAT_DTYPE_FP16 && a.dtype != PAT_DTYPE_BF16) return PAT_ERR_UNSUPPORTED;
+    if (a.page_size < 16 || a.page_size % 16 != 0 || a.page_size > 256) return PAT_ERR_UNSUPPORTED;
+    if (a.work.hratio < 1 || a.work.hratio > 16) return PAT_ERR_UNSUPPORTED;
+    if (!(a.softmax_scale > 0.f) || !std::isfinite(a.softmax_scale)) return PAT_ERR_BAD_ARGUMENT;
+    // TMA: 16-byte aligned bases and strides; Q/O rows are read and written with vector accesses
+    if (!aligned16(a.k_cache) || !aligned16(a.v_cache) || !aligned16(a.q) || !aligned16(a.out))
+        return PAT_ERR_UNSUPPORTED;
+    const int64_t strides[] = {a.k_page_stride, a.k_row_stride, a.k_head_stride, a.v_page_stride, a.v_row_stride,
+                               a.v_head_stride, a.q_batch_stride, a.q_head_stride, a.out_batch_stride,
+                               a.out_head_stride};
+    for (int64_t s : strides)
+        if (s <= 0 || s % 8 != 0) return PAT_ERR_UNSUPPORTED;
+    if (!aligned16(a.work_blob)) return PAT_ERR_BAD_ARGUMENT;
+    const size_t need = pat_b200_workspace_bytes(&a.work, a.num_q_heads, a.head_dim);
+    if (a.work.num_entries > 0 && (!a.workspace || a.workspace_bytes < need || !aligned16(a.workspace)))
+        return PAT_ERR_WORKSPACE;
+
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return PAT_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return PAT_ERR_UNSUPPORTED;
+    static thread_local int checked_dev = -1;
+    if (checked_dev != dev) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return PAT_ERR_CUDA;
+        if (major != 10) return PAT_ERR_NO_DEVICE_CODE;
+        checked_dev = dev;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    const bool bf16 = a.dtype == PAT_DTYPE_BF16;
+    if (a.head_dim == 128)
+        return bf16 ? launch_all<__nv_bfloat16, 128>(a, stream, dev) : launch_all<__half, 128>(a, stream, dev);
+    return bf16 ? launch_all<__nv_bfloat16, 64>(a, stream, dev) : launch_all<__half, 64>(a, stream, dev);
+}
+
+}  // extern "C"

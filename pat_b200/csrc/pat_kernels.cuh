@@ -1,0 +1,438 @@
+// Attention kernels of the decode path (sm_100a): streaming tiles, dense tiles
+// and the log-sum-exp merge.
+//
+// Work items are produced on the host (pat_work.h).  One CTA = one item x one
+// KV head; blockIdx.x = item * kv_heads + kv_head, so the KV heads of an item
+// (which touch the same pages, 256 B apart) run next to each other.
+//
+//   stream_kernel : <= 16 query rows (the GQA group of 1-2 requests).  HBM-bound.
+//                   Every warp owns a private multi-stage TMA pipeline over its
+//                   share of the item's 16-token sub-tiles - no CTA-wide barrier
+//                   in the main loop - and the warps' partial softmax states are
+//                   combined through shared memory at the end.
+//   dense_kernel  : up to 128 query rows sharing one KV segment.  A producer warp
+//                   streams 64-token K/V stages by TMA; eight consumer warps own
+//                   16 rows each and read every staged tile once from shared
+//                   memory, so a shared page is fetched once per 128 rows.
+//   merge_kernel  : one warp per (request, head): out = sum_i e^(lse_i-lse) O_i.
+//
+// All kernels replace csrc/pat_fwd_kernel.h (pat_kernel :25-299, gather_kernel
+// :314-467) of the reference.
+#pragma once
+
+#include "pat_device.cuh"
+#include "pat_work.h"
+
+namespace pat {
+
+struct AttnParams {
+    const void* q;
+    float* part_o;        // [entries, H, D]
+    float* part_lse;      // [entries, H]
+    const int32_t* items;     // WorkItem[...]
+    const int32_t* queries;
+    const int32_t* pages;
+    int64_t q_batch_stride, q_head_stride;
+    int num_items;
+    int kv_heads;
+    int hratio;
+    int num_q_heads;
+    int page_size;
+    float scale;          // softmax scale
+    float scale_log2;     // scale * log2(e)
+    int32_t* status;      // optional
+};
+
+constexpr int kStreamWarps = 4;
+constexpr int kStreamStages = 3;
+constexpr int kDenseWarps = 8;          // consumer warps (16 rows each)
+constexpr int kDenseStages = 3;
+constexpr int kDenseSub = 4;            // 16-token sub-tiles per dense stage (64 tokens)
+constexpr int kScratchPad = 8;          // floats of padding per scratch row
+
+template <int D> constexpr int stream_smem_bytes() {
+    return kStreamWarps * kStreamStages * TileGeom<D>::kSubBytes + 1024;
+}
+template <int D> constexpr int dense_smem_bytes() {
+    return kDenseStages * kDenseSub * TileGeom<D>::kSubBytes + 1024;
+}
+
+// Q rows of one 16-row tile straight into mma A fragments.
+template <typename T, int D>
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], const AttnParams& p, const int32_t* qids,
+                                             int row_base, int rows_valid, int kvh, int lane) {
+    const T* q = static_cast<const T*>(p.q);
+    const int r0 = row_base + (lane >> 2), r1 = r0 + 8;
+    const T* p0 = nullptr;
+    const T* p1 = nullptr;
+    if (r0 < rows_valid) {
+        const int qi = r0 / p.hratio, g = r0 - qi * p.hratio;
+        p0 = q + static_cast<int64_t>(__ldg(qids + qi)) * p.q_batch_stride +
+             static_cast<int64_t>(kvh * p.hratio + g) * p.q_head_stride;
+    }
+    if (r1 < rows_valid) {
+        const int qi = r1 / p.hratio, g = r1 - qi * p.hratio;
+        p1 = q + static_cast<int64_t>(__ldg(qids + qi)) * p.q_batch_stride +
+             static_cast<int64_t>(kvh * p.hratio + g) * p.q_head_stride;
+    }
+    const int col = (lane & 3) << 1;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        qf[ks][0] = p0 ? __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + col)) : 0u;
+        qf[ks][1] = p1 ? __ldg(reinterpret_cast<const uint32_t*>(p1 + ks * 16 + col)) : 0u;
+        qf[ks][2] = p0 ? __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8 + col)) : 0u;
+        qf[ks][3] = p1 ? __ldg(reinterpret_cast<const uint32_t*>(p1 + ks * 16 + 8 + col)) : 0u;
+    }
+}
+
+// ------------------------------------------------------------------------------
+// Streaming kernel
+// ------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kStreamWarps * 32)
+stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    using G = TileGeom<D>;
+    constexpr int W = kStreamWarps, S = kStreamStages;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t bars[W * S];
+    __shared__ float sm_m[W][16], sm_l[W][16];
+    __shared__ int sm_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int item_idx = blockIdx.x / p.kv_heads;
+    const int kvh = blockIdx.x - item_idx * p.kv_heads;
+    const int32_t* it = p.items + static_cast<size_t>(item_idx) * 8;
+    const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
+              entry_base = __ldg(it + 4);
+    const int rows_valid = nq * p.hratio;
+
+    if (tid == 0) {
+        sm_abort = 0;
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        for (int i = 0; i < W * S; ++i) mbar_init(smem_u32(&bars[i]), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int n_tiles = (kv_len + 15) >> 4;
+    const int my_n = warp < n_tiles ? (n_tiles - warp + W - 1) / W : 0;
+    const int tiles_per_page = p.page_size >> 4;
+    unsigned char* my_stage = smem + static_cast<size_t>(warp) * S * G::kSubBytes;
+    const uint32_t my_stage_addr = smem_u32(my_stage);
+    const uint32_t my_bar = smem_u32(&bars[warp * S]);
+    const int32_t* item_pages = p.pages + page_off;
+
+    // page ids of my next 32 tiles, one per lane
+    auto fetch_ids = [&](int jbase) -> int {
+        const int j = jbase + lane;
+        if (j >= my_n) return 0;
+        const int t = warp + j * W;
+        return __ldg(item_pages + t / tiles_per_page);
+    };
+    int ids_cur = fetch_ids(0);
+    int ids_next = fetch_ids(32);
+
+    auto issue = [&](int j, int page) {   // lane 0 only
+        const int t = warp + j * W;
+        const int row0 = (t % tiles_per_page) << 4;
+        const int s = j % S;
+        const uint32_t bar = my_bar + s * 8;
+        const uint32_t dst = my_stage_addr + s * G::kSubBytes;
+        mbar_expect_tx(bar, G::kSubBytes);
+#pragma unroll
+        for (int b = 0; b < G::kBoxes; ++b) {
+            tma_load_4d(dst + b * 2048, &kmap, bar, b * 64, kvh, row0, page);
+            tma_load_4d(dst + G::kOperandBytes + b * 2048, &vmap, bar, b * 64, kvh, row0, page);
+        }
+    };
+
+#pragma unroll
+    for (int j = 0; j < S; ++j) {
+        const int page = __shfl_sync(kFullMask, ids_cur, j);
+        if (j < my_n && lane == 0) issue(j, page);
+    }
+
+    uint32_t qf[D / 16][4];
+    load_q_frags<T, D>(qf, p, p.queries + q_off, 0, rows_valid, kvh, lane);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    bool ok = true;
+
+    for (int j = 0; j < my_n; ++j) {
+        const int s = j % S;
+        if (!mbar_wait(my_bar + s * 8, (j / S) & 1)) { ok = false; break; }
+        const int t = warp + j * W;
+        const int valid = min(16, kv_len - (t << 4));
+        if (valid < 16) {
+            zero_v_tail<D>(my_stage + s * G::kSubBytes, 0, valid, lane);
+            __syncwarp();
+        }
+        warp_attend_tile<T, D, 1>(qf, o, m, l, my_stage_addr + s * G::kSubBytes, valid, p.scale_log2, lane);
+        __syncwarp();
+        const int jn = j + S;
+        if ((jn & 31) == 0) { ids_cur = ids_next; ids_next = fetch_ids(jn + 32); }
+        const int page = __shfl_sync(kFullMask, ids_cur, jn & 31);
+        if (jn < my_n && lane == 0) issue(jn, page);
+    }
+    if (!ok) {
+        if (lane == 0) { sm_abort = 1; if (p.status) atomicExch(p.status, 1); }
+    }
+
+    // ---- combine the warps' partial states --------------------------------------
+    l[0] += __shfl_xor_sync(kFullMask, l[0], 1);
+    l[0] += __shfl_xor_sync(kFullMask, l[0], 2);
+    l[1] += __shfl_xor_sync(kFullMask, l[1], 1);
+    l[1] += __shfl_xor_sync(kFullMask, l[1], 2);
+    if ((lane & 3) == 0) {
+        sm_m[warp][lane >> 2] = m[0];
+        sm_m[warp][(lane >> 2) + 8] = m[1];
+        sm_l[warp][lane >> 2] = l[0];
+        sm_l[warp][(lane >> 2) + 8] = l[1];
+    }
+    __syncthreads();   // every warp is done with its pipeline memory
+    if (sm_abort) return;
+
+    constexpr int kRowStride = D + kScratchPad;
+    float* scratch = reinterpret_cast<float*>(smem);     // [W][16][D + pad]
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8;
+        float g0 = -INFINITY, g1 = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < W; ++w) { g0 = fmaxf(g0, sm_m[w][r0]); g1 = fmaxf(g1, sm_m[w][r1]); }
+        const float f0 = (m[0] == -INFINITY) ? 0.f : fast_exp2((m[0] - g0) * p.scale_log2);
+        const float f1 = (m[1] == -INFINITY) ? 0.f : fast_exp2((m[1] - g1) * p.scale_log2);
+        float* base = scratch + static_cast<size_t>(warp) * 16 * kRowStride;
+        const int col = (lane & 3) << 1;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            *reinterpret_cast<float2*>(base + r0 * kRowStride + i * 8 + col) = make_float2(o[i][0] * f0, o[i][1] * f0);
+            *reinterpret_cast<float2*>(base + r1 * kRowStride + i * 8 + col) = make_float2(o[i][2] * f1, o[i][3] * f1);
+        }
+    }
+    __syncthreads();
+
+    constexpr int kVec = D / 4;   // float4 per row
+    for (int idx = tid; idx < rows_valid * kVec; idx += W * 32) {
+        const int row = idx / kVec, v4 = idx - row * kVec;
+        float g = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < W; ++w) g = fmaxf(g, sm_m[w][row]);
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < W; ++w) {
+            const float mw = sm_m[w][row];
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2((mw - g) * p.scale_log2);
+            L += sm_l[w][row] * f;
+            const float4 x = *reinterpret_cast<const float4*>(scratch + (static_cast<size_t>(w) * 16 + row) * kRowStride + v4 * 4);
+            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        const float inv = 1.f / L;
+        const int qi = row / p.hratio, gg = row - qi * p.hratio;
+        const size_t slot = static_cast<size_t>(entry_base + qi) * p.num_q_heads + kvh * p.hratio + gg;
+        *reinterpret_cast<float4*>(p.part_o + slot * D + v4 * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        if (v4 == 0) p.part_lse[slot] = g * p.scale + logf(L);
+    }
+}
+
+// ------------------------------------------------------------------------------
+// Dense kernel (mma.sync tiles; 8 consumer warps x 16 rows + 1 producer warp)
+// ------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__((kDenseWarps + 1) * 32)
+dense_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    using G = TileGeom<D>;
+    constexpr int W = kDenseWarps, S = kDenseStages, U = kDenseSub;
+    constexpr int kStageBytes = U * G::kSubBytes;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int item_idx = blockIdx.x / p.kv_heads;
+    const int kvh = blockIdx.x - item_idx * p.kv_heads;
+    const int32_t* it = p.items + static_cast<size_t>(item_idx) * 8;
+    const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
+              entry_base = __ldg(it + 4);
+    const int rows_valid = nq * p.hratio;
+
+    if (tid == 0) {
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        for (int i = 0; i < S; ++i) {
+            mbar_init(smem_u32(&full_bar[i]), 1);
+            mbar_init(smem_u32(&empty_bar[i]), W);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int n_sub = (kv_len + 15) >> 4;           // 16-token sub-tiles
+    const int n_stage_tiles = (n_sub + U - 1) / U;  // 64-token stages
+    const int tiles_per_page = p.page_size >> 4;
+    const int32_t* item_pages = p.pages + page_off;
+    const uint32_t smem_addr = smem_u32(smem);
+
+    if (warp == W) {
+        // ---- producer warp ------------------------------------------------------
+        for (int j = 0; j < n_stage_tiles; ++j) {
+            const int s = j % S;
+            if (j >= S) {
+                if (!mbar_wait(smem_u32(&empty_bar[s]), ((j / S) - 1) & 1)) {
+                    if (lane == 0 && p.status) atomicExch(p.status, 2);
+                    return;
+                }
+            }
+            const int subs = min(U, n_sub - j * U);
+            // lanes 0..subs-1 each fetch one page id and issue the boxes of one sub-tile
+            if (lane == 0) mbar_expect_tx(smem_u32(&full_bar[s]), subs * G::kSubBytes);
+            __syncwarp();
+            if (lane < subs) {
+                const int t = j * U + lane;
+                const int page = __ldg(item_pages + t / tiles_per_page);
+                const int row0 = (t % tiles_per_page) << 4;
+                const uint32_t dst = smem_addr + s * kStageBytes + lane * G::kSubBytes;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+#pragma unroll
+                for (int b = 0; b < G::kBoxes; ++b) {
+                    tma_load_4d(dst + b * 2048, &kmap, bar, b * 64, kvh, row0, page);
+                    tma_load_4d(dst + G::kOperandBytes + b * 2048, &vmap, bar, b * 64, kvh, row0, page);
+                }
+            }
+            __syncwarp();
+        }
+        return;
+    }
+
+    // ---- consumer warps -----------------------------------------------------------
+    const int row_base = warp * 16;
+    const bool active = row_base < rows_valid;   // warps without rows still release stages
+    uint32_t qf[D / 16][4];
+    load_q_frags<T, D>(qf, p, p.queries + q_off, row_base, rows_valid, kvh, lane);
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int j = 0; j < n_stage_tiles; ++j) {
+        const int s = j % S;
+        if (!mbar_wait(smem_u32(&full_bar[s]), (j / S) & 1)) {
+            if (lane == 0 && p.status) atomicExch(p.status, 3);
+            return;
+        }
+        const int subs = min(U, n_sub - j * U);
+        const int valid = min(16 * U, kv_len - j * 16 * U);
+        const uint32_t stage = smem_addr + s * kStageBytes;
+        if (active) {
+            if (subs == U) {
+                if (valid < 16 * U) {
+                    // only reached on the last stage: the tail sub-tile holds garbage rows
+                    // (each consumer zeroes its own view; same values, benign duplication)
+                    zero_v_tail<D>(smem + s * kStageBytes, U - 1, valid - 16 * (U - 1), lane);
+                    __syncwarp();
+                }
+                warp_attend_tile<T, D, U>(qf, o, m, l, stage, valid, p.scale_log2, lane);
+            } else {
+                for (int u = 0; u < subs; ++u) {
+                    const int v = min(16, valid - 16 * u);
+                    if (v < 16) {
+                        zero_v_tail<D>(smem + s * kStageBytes, u, v, lane);
+                        __syncwarp();
+                    }
+                    warp_attend_tile<T, D, 1>(qf, o, m, l, stage + u * G::kSubBytes, v, p.scale_log2, lane);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+    }
+
+    if (!active) return;
+    l[0] += __shfl_xor_sync(kFullMask, l[0], 1);
+    l[0] += __shfl_xor_sync(kFullMask, l[0], 2);
+    l[1] += __shfl_xor_sync(kFullMask, l[1], 1);
+    l[1] += __shfl_xor_sync(kFullMask, l[1], 2);
+    const int col = (lane & 3) << 1;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = row_base + (lane >> 2) + 8 * h;
+        if (row >= rows_valid) continue;
+        const int qi = row / p.hratio, gg = row - qi * p.hratio;
+        const size_t slot = static_cast<size_t>(entry_base + qi) * p.num_q_heads + kvh * p.hratio + gg;
+        const float inv = 1.f / l[h];
+        float* dst = p.part_o + slot * D + col;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+        if ((lane & 3) == 0) p.part_lse[slot] = m[h] * p.scale + logf(l[h]);
+    }
+}
+
+// ------------------------------------------------------------------------------
+// Merge kernel: one warp per (request, query head)
+// ------------------------------------------------------------------------------
+struct MergeParams {
+    const float* part_o;
+    const float* part_lse;
+    const int32_t* indptr;    // [batch + 1]
+    const int32_t* entries;
+    void* out;
+    float* lse_out;           // optional [batch, H]
+    int64_t out_batch_stride, out_head_stride;
+    int batch, num_q_heads;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
+    constexpr int kPer = D / 32;   // floats per lane
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= p.batch * p.num_q_heads) return;
+    const int b = row / p.num_q_heads, h = row - b * p.num_q_heads;
+    const int lo = __ldg(p.indptr + b), n = __ldg(p.indptr + b + 1) - lo;
+    const int32_t* ent = p.entries + lo;
+
+    float gmax = -INFINITY;
+    for (int i = lane; i < n; i += 32)
+        gmax = fmaxf(gmax, __ldg(p.part_lse + static_cast<size_t>(__ldg(ent + i)) * p.num_q_heads + h));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(kFullMask, gmax, d));
+
+    float acc[kPer];
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) acc[k] = 0.f;
+    float wsum = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const size_t slot = static_cast<size_t>(__ldg(ent + i)) * p.num_q_heads + h;
+        const float lse = __ldg(p.part_lse + slot);
+        const float w = (lse == -INFINITY) ? 0.f : __expf(lse - gmax);
+        wsum += w;
+        const float* src = p.part_o + slot * D + lane * kPer;
+        if constexpr (kPer == 4) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(src));
+            acc[0] += w * x.x; acc[1] += w * x.y; acc[2] += w * x.z; acc[3] += w * x.w;
+        } else {
+            const float2 x = __ldg(reinterpret_cast<const float2*>(src));
+            acc[0] += w * x.x; acc[1] += w * x.y;
+        }
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    T* dst = static_cast<T*>(p.out) + static_cast<int64_t>(b) * p.out_batch_stride +
+             static_cast<int64_t>(h) * p.out_head_stride + lane * kPer;
+    if constexpr (kPer == 4) {
+        uint2 v;
+        v.x = Elt<T>::pack(acc[0] * inv, acc[1] * inv);
+        v.y = Elt<T>::pack(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2*>(dst) = v;
+    } else {
+        *reinterpret_cast<uint32_t*>(dst) = Elt<T>::pack(acc[0] * inv, acc[1] * inv);
+    }
+    if (p.lse_out && lane == 0) p.lse_out[row] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+}
+
+}  // namespace pat

@@ -1,0 +1,301 @@
+// Work-list builder; see pat_work.h.
+#include "pat_work.h"
+
+#include <algorithm>
+#include <cstring>
+#include <numeric>
+#include <unordered_map>
+
+namespace pat {
+
+namespace {
+
+inline uint64_t mix64(uint64_t h, uint64_t v) {
+    h ^= v + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2);
+    h *= 0xff51afd7ed558ccdULL;
+    h ^= h >> 33;
+    return h;
+}
+
+struct FusedBox {            // boxes that share one page list
+    const int32_t* pages;
+    int num_pages;
+    int kv_len;
+    std::vector<int32_t> queries;
+};
+
+struct Segment {             // pages attended by exactly the same fused boxes
+    std::vector<int32_t> queries;
+    std::vector<int32_t> pages;
+    int64_t tokens = 0;
+    int partial_tokens = 0;  // valid tokens of the (single, last) partial page, 0 if none
+    int32_t q_off = 0, page_off = 0;
+};
+
+inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace
+
+int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, int hratio, int kv_heads,
+                    int page_size, int64_t num_cache_pages, const WorkOptions& opt) {
+    header_ = WorkHeader{};
+    blob_.clear();
+    if (num_buckets < 0 || batch <= 0 || hratio < 1 || hratio > 16 || kv_heads < 1 || page_size < 16 ||
+        page_size % 16 != 0 || opt.stream_rows < hratio || (num_buckets > 0 && !buckets))
+        return -1;
+
+    // ---- 1. fuse boxes with identical page lists -----------------------------
+    std::vector<FusedBox> fused;
+    std::unordered_map<uint64_t, std::vector<int>> by_hash;
+    for (int b = 0; b < num_buckets; ++b) {
+        const PlanBucketView& bk = buckets[b];
+        for (int c = 0; c < bk.ctas; ++c) {
+            const int nq = bk.num_seqs[c];
+            const int kv = bk.kv_lens[c];
+            if (nq <= 0 || kv <= 0) continue;   // nothing to attend: contributes no partial
+            const int np = ceil_div(kv, page_size);
+            if (nq > bk.q_stride || np > bk.block_stride) return -2;
+            const int32_t* q = bk.q_table + static_cast<size_t>(c) * bk.q_stride;
+            const int32_t* pg = bk.block_table + static_cast<size_t>(c) * bk.block_stride;
+            for (int i = 0; i < nq; ++i)
+                if (q[i] < 0 || q[i] >= batch) return -3;
+            uint64_t h = mix64(0x1234, static_cast<uint64_t>(kv));
+            for (int i = 0; i < np; ++i) {
+                if (pg[i] < 0 || (num_cache_pages > 0 && pg[i] >= num_cache_pages)) return -4;
+                h = mix64(h, static_cast<uint64_t>(pg[i]));
+            }
+            int found = -1;
+            auto& cand = by_hash[h];
+            for (int g : cand) {
+                const FusedBox& f = fused[g];
+                if (f.num_pages == np && f.kv_len == kv && std::memcmp(f.pages, pg, sizeof(int32_t) * np) == 0) {
+                    found = g;
+                    break;
+                }
+            }
+            if (found < 0) {
+                found = static_cast<int>(fused.size());
+                fused.push_back(FusedBox{pg, np, kv, {}});
+                cand.push_back(found);
+            }
+            fused[found].queries.insert(fused[found].queries.end(), q, q + nq);
+        }
+    }
+
+    // ---- 2. which fused boxes contain each (page, valid) ---------------------
+    // Signatures are kept as linked lists in a flat pool; their hash is updated
+    // as boxes are appended (boxes are visited in increasing order, so equal
+    // sets give equal sequences).
+    std::unordered_map<uint64_t, int> slot_of;   // (page << 32 | valid) -> slot
+    std::vector<uint64_t> slot_key, slot_hash;
+    std::vector<int> slot_head, slot_tail, slot_len;
+    std::vector<int> link_box, link_next;
+    slot_of.reserve(1024);
+    for (int g = 0; g < static_cast<int>(fused.size()); ++g) {
+        const FusedBox& f = fused[g];
+        for (int p = 0; p < f.num_pages; ++p) {
+            const int valid = (p == f.num_pages - 1) ? f.kv_len - p * page_size : page_size;
+            const uint64_t key = (static_cast<uint64_t>(static_cast<uint32_t>(f.pages[p])) << 32) |
+                                 static_cast<uint32_t>(valid);
+            auto ins = slot_of.emplace(key, static_cast<int>(slot_key.size()));
+            int s = ins.first->second;
+            if (ins.second) {
+                slot_key.push_back(key);
+                slot_hash.push_back(0x9876);
+                slot_head.push_back(-1);
+                slot_tail.push_back(-1);
+                slot_len.push_back(0);
+            }
+            const int link = static_cast<int>(link_box.size());
+            link_box.push_back(g);
+            link_next.push_back(-1);
+            if (slot_tail[s] >= 0) link_next[slot_tail[s]] = link; else slot_head[s] = link;
+            slot_tail[s] = link;
+            slot_len[s] += 1;
+            slot_hash[s] = mix64(slot_hash[s], static_cast<uint64_t>(g));
+        }
+    }
+
+    // ---- 3. segments = slots with the same signature -------------------------
+    std::vector<Segment> segs;
+    std::vector<int> seg_rep;   // a representative slot per segment (for comparing signatures)
+    std::unordered_map<uint64_t, std::vector<int>> seg_by_hash;
+    auto same_sig = [&](int a, int b) {
+        if (slot_len[a] != slot_len[b]) return false;
+        int la = slot_head[a], lb = slot_head[b];
+        while (la >= 0) {
+            if (link_box[la] != link_box[lb]) return false;
+            la = link_next[la];
+            lb = link_next[lb];
+        }
+        return true;
+    };
+    for (int s = 0; s < static_cast<int>(slot_key.size()); ++s) {
+        const int valid = static_cast<int>(slot_key[s] & 0xffffffffu);
+        const int32_t page = static_cast<int32_t>(slot_key[s] >> 32);
+        // a partial page always gets a segment key of its own signature hash so that
+        // two partial pages never land in one segment
+        uint64_t h = slot_hash[s];
+        auto& cand = seg_by_hash[h];
+        int seg = -1;
+        for (int c : cand) {
+            if (same_sig(seg_rep[c], s) && !(valid < page_size && segs[c].partial_tokens > 0)) {
+                seg = c;
+                break;
+            }
+        }
+        if (seg < 0) {
+            seg = static_cast<int>(segs.size());
+            segs.emplace_back();
+            seg_rep.push_back(s);
+            cand.push_back(seg);
+            for (int l = slot_head[s]; l >= 0; l = link_next[l]) {
+                const auto& q = fused[link_box[l]].queries;
+                segs[seg].queries.insert(segs[seg].queries.end(), q.begin(), q.end());
+            }
+        }
+        Segment& sg = segs[seg];
+        if (valid < page_size) {
+            sg.partial_tokens = valid;      // appended after the loop, so that it is last
+            sg.pages.push_back(-1 - page);  // marker, fixed below
+        } else {
+            sg.pages.push_back(page);
+        }
+        sg.tokens += valid;
+    }
+    for (Segment& sg : segs) {
+        if (sg.partial_tokens > 0) {
+            auto it = std::find_if(sg.pages.begin(), sg.pages.end(), [](int32_t v) { return v < 0; });
+            const int32_t page = -1 - *it;
+            sg.pages.erase(it);
+            sg.pages.push_back(page);
+        }
+    }
+
+    // ---- 4. chunk sizes -------------------------------------------------------
+    const int q_per_stream = std::max(1, opt.stream_rows / hratio);
+    const int q_per_dense = opt.dense_rows > 0 ? std::max(1, opt.dense_rows / hratio) : 0;
+    auto is_dense = [&](const Segment& sg) {
+        return q_per_dense > 0 && static_cast<int64_t>(sg.queries.size()) * hratio >= opt.dense_min_rows;
+    };
+    int64_t stream_cost = 0, dense_cost = 0, unique_tokens = 0;
+    for (const Segment& sg : segs) {
+        unique_tokens += sg.tokens;
+        const int nq = static_cast<int>(sg.queries.size());
+        if (is_dense(sg)) dense_cost += sg.tokens * ceil_div(nq, q_per_dense);
+        else stream_cost += sg.tokens * ceil_div(nq, q_per_stream);
+    }
+    auto pick_chunk = [&](int64_t cost, int cmin, int cmax, int per_sm) {
+        int64_t want = cost * kv_heads / std::max<int64_t>(1, static_cast<int64_t>(opt.num_sms) * per_sm);
+        want = (want + page_size - 1) / page_size * page_size;
+        want = std::max<int64_t>(want, std::max(cmin, page_size));
+        want = std::min<int64_t>(want, std::max(cmax, page_size));
+        return static_cast<int>(want);
+    };
+    const int stream_chunk = pick_chunk(stream_cost, opt.chunk_tokens_min, opt.chunk_tokens_max, opt.items_per_sm);
+    const int dense_chunk = pick_chunk(dense_cost, opt.chunk_tokens_min, opt.dense_chunk_tokens_max,
+                                       std::max(1, opt.items_per_sm / 4));
+
+    // ---- 5. items -------------------------------------------------------------
+    std::vector<int32_t> queries_sec, pages_sec;
+    for (Segment& sg : segs) {
+        sg.q_off = static_cast<int32_t>(queries_sec.size());
+        queries_sec.insert(queries_sec.end(), sg.queries.begin(), sg.queries.end());
+        sg.page_off = static_cast<int32_t>(pages_sec.size());
+        pages_sec.insert(pages_sec.end(), sg.pages.begin(), sg.pages.end());
+    }
+    std::vector<WorkItem> stream_items, dense_items;
+    int32_t num_entries = 0;
+    std::vector<int32_t> per_query(batch, 0);
+    for (const Segment& sg : segs) {
+        const bool dense = is_dense(sg);
+        const int nq = static_cast<int>(sg.queries.size());
+        const int qpi = dense ? q_per_dense : q_per_stream;
+        const int chunk = dense ? dense_chunk : stream_chunk;
+        const int np = static_cast<int>(sg.pages.size());
+        const int kparts = std::max(1, ceil_div(sg.tokens, chunk));
+        const int ppc = ceil_div(np, kparts);            // pages per KV chunk
+        for (int p0 = 0; p0 < np; p0 += ppc) {
+            const int p1 = std::min(np, p0 + ppc);
+            const int64_t tok_lo = static_cast<int64_t>(p0) * page_size;
+            const int kv = static_cast<int>(std::min<int64_t>(sg.tokens - tok_lo,
+                                                              static_cast<int64_t>(p1 - p0) * page_size));
+            for (int q0 = 0; q0 < nq; q0 += qpi) {
+                WorkItem it{};
+                it.q_off = sg.q_off + q0;
+                it.nq = std::min(qpi, nq - q0);
+                it.page_off = sg.page_off + p0;
+                it.kv_len = kv;
+                it.entry_base = num_entries;
+                it.kind = dense ? 1 : 0;
+                it.cost = kv;
+                num_entries += it.nq;
+                for (int i = 0; i < it.nq; ++i) per_query[sg.queries[q0 + i]] += 1;
+                (dense ? dense_items : stream_items).push_back(it);
+                if (dense) header_.dense_tokens += kv; else header_.stream_tokens += kv;
+            }
+        }
+    }
+    auto by_cost = [](const WorkItem& a, const WorkItem& b) { return a.cost > b.cost; };
+    std::stable_sort(stream_items.begin(), stream_items.end(), by_cost);
+    std::stable_sort(dense_items.begin(), dense_items.end(), by_cost);
+
+    // ---- 6. merge lists -------------------------------------------------------
+    std::vector<int32_t> indptr(batch + 1, 0);
+    for (int b = 0; b < batch; ++b) indptr[b + 1] = indptr[b] + per_query[b];
+    std::vector<int32_t> fill(indptr.begin(), indptr.end() - 1);
+    std::vector<int32_t> entries(num_entries, 0);
+    auto scatter = [&](const std::vector<WorkItem>& items) {
+        for (const WorkItem& it : items)
+            for (int i = 0; i < it.nq; ++i) entries[fill[queries_sec[it.q_off + i]]++] = it.entry_base + i;
+    };
+    scatter(stream_items);
+    scatter(dense_items);
+    // deterministic merge order: ascending entry id per query
+    int max_per_query = 0;
+    for (int b = 0; b < batch; ++b) {
+        std::sort(entries.begin() + indptr[b], entries.begin() + indptr[b + 1]);
+        max_per_query = std::max(max_per_query, per_query[b]);
+    }
+
+    // ---- 7. blob --------------------------------------------------------------
+    const size_t n_items = stream_items.size() + dense_items.size();
+    auto align8 = [](size_t v) { return (v + 7) / 8 * 8; };
+    const size_t items_off = 0;
+    const size_t queries_off = align8(items_off + n_items * 8);
+    const size_t pages_off = align8(queries_off + queries_sec.size());
+    const size_t indptr_off = align8(pages_off + pages_sec.size());
+    const size_t entries_off = align8(indptr_off + indptr.size());
+    const size_t total = align8(entries_off + entries.size()) + 8;
+    blob_.assign(total, 0);
+    if (!stream_items.empty())
+        std::memcpy(blob_.data() + items_off, stream_items.data(), stream_items.size() * sizeof(WorkItem));
+    if (!dense_items.empty())
+        std::memcpy(blob_.data() + items_off + stream_items.size() * 8, dense_items.data(),
+                    dense_items.size() * sizeof(WorkItem));
+    std::copy(queries_sec.begin(), queries_sec.end(), blob_.begin() + queries_off);
+    std::copy(pages_sec.begin(), pages_sec.end(), blob_.begin() + pages_off);
+    std::copy(indptr.begin(), indptr.end(), blob_.begin() + indptr_off);
+    std::copy(entries.begin(), entries.end(), blob_.begin() + entries_off);
+
+    header_.batch = batch;
+    header_.hratio = hratio;
+    header_.page_size = page_size;
+    header_.num_stream_items = static_cast<int32_t>(stream_items.size());
+    header_.num_dense_items = static_cast<int32_t>(dense_items.size());
+    header_.num_entries = num_entries;
+    header_.max_entries_per_query = max_per_query;
+    header_.items_off = static_cast<int32_t>(items_off);
+    header_.queries_off = static_cast<int32_t>(queries_off);
+    header_.pages_off = static_cast<int32_t>(pages_off);
+    header_.merge_indptr_off = static_cast<int32_t>(indptr_off);
+    header_.merge_entries_off = static_cast<int32_t>(entries_off);
+    header_.blob_words = static_cast<int32_t>(total);
+    header_.num_segments = static_cast<int32_t>(segs.size());
+    header_.max_page_id = -1;
+    for (int32_t pg : pages_sec) header_.max_page_id = std::max(header_.max_page_id, pg);
+    header_.unique_tokens = unique_tokens;
+    return 0;
+}
+
+}  // namespace pat
