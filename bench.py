@@ -1,0 +1,387 @@
+"""Decode-attention benchmark: microseconds per decode step and fraction of the HBM roofline
+on deduplicated KV bytes, for the synthetic prefix-tree workloads of pat_b200/workloads.py.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+One process per GPU.  With N > 1 the KV heads (and their query heads) are sharded across the
+ranks; there is no data-path collective.  Rank 0 prints one JSON line.
+
+A "step" is one call of the public op ``prefix_attn_with_kvcache`` (all kernels of one decode
+step of one layer) on the same resident paged KV cache.  ``value`` times the kernels with CUDA
+events; ``e2e`` additionally moves the step's host inputs (queries, plan tables / work list)
+to the device and the output back inside the timed region.  The KV cache itself is state that
+lives on the GPU across steps (a decode step appends one token per request), so it is not
+copied per step.
+
+``--impl reference`` times the reference's own attention path - dense fp32 PyTorch attention
+per request on the host cores (the CPU restatement in oracle/attention_oracle.py of
+test/utils.py::attention_ref) - on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_attn_us_per_step"
+UNIT = "us"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", type=int, default=4, help="workload 0..4 (default: long-context mixed batch)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float):
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 7] or \
+               [r for _, r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        mhz = sorted(float(r[0]) for r in rows if r[0].replace(".", "", 1).isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "", 1).isdigit() else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def cpu_attention_sample(w, q_cpu, k_rows, budget_s, order):
+    """Dense fp32 attention per request on the host cores for as many requests (in ``order``)
+    as fit in ``budget_s``.  ``k_rows(b)`` returns the request's dense (K, V) fp32 on the CPU.
+    Returns (seconds, tokens, requests)."""
+    import torch
+    from oracle import attention_oracle as O
+    spent, tokens, done = 0.0, 0, 0
+    for b in order:
+        kk, vv = k_rows(b)
+        t0 = time.perf_counter()
+        O.dense_attention(q_cpu[b:b + 1], kk[None], vv[None], None, None)
+        spent += time.perf_counter() - t0
+        tokens += w.seq_lens[b]
+        done += 1
+        if spent >= budget_s:
+            break
+    return spent, tokens, done
+
+
+def main():
+    args = parse()
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py --gpus {args.gpus} must be launched with torch.distributed.run "
+                  f"(--nproc-per-node {args.gpus})", file=sys.stderr)
+            sys.exit(2)
+    n = world
+
+    from pat_b200.workloads import make_config, torch_dtype
+    w = make_config(args.config)
+    if w.num_kv_heads % n != 0:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "unavailable": f"{w.num_kv_heads} KV heads do not shard over {n} GPUs"}))
+        return
+    hk = w.num_kv_heads // n
+    hq = hk * w.group
+    D, page, B = w.head_dim, w.page_size, w.batch
+    scale = 1.0 / math.sqrt(D)
+    dt = torch_dtype(w.dtype)
+    workload_name = f"{w.name}: {w.description}; {w.num_q_heads}/{w.num_kv_heads} heads, D={D}, {w.dtype}, {page}-token pages"
+    config = {"workload": workload_name, "batch": B, "unique_tokens": w.unique_tokens,
+              "total_tokens": w.total_tokens, "kv_head_shards": n,
+              "l2": "inputs larger than L2 (per-GPU KV bytes >> 126 MB); no flush between steps"}
+    bytes_total = w.dedup_kv_bytes()
+    bytes_rank = w.dedup_kv_bytes(kv_heads=hk, q_heads=hq)
+    if bytes_rank < 4 * 126e6:
+        config["l2"] = "per-GPU KV bytes are below 4x L2: a 512 MB buffer is written between steps to flush L2"
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        gen = torch.Generator().manual_seed(w.seed)
+        q_cpu = (torch.randn(B, 1, w.num_q_heads, D, generator=gen) * 0.5).to(dt).float()
+        rng = np.random.default_rng(0)
+        order = rng.permutation(B).tolist()
+
+        def rows(b):
+            g = torch.Generator().manual_seed(1000 + b)
+            L = w.seq_lens[b]
+            kk = (torch.randn(L, w.num_kv_heads, D, generator=g) * 0.5).to(dt).float()
+            vv = (torch.randn(L, w.num_kv_heads, D, generator=g) * 0.5).to(dt).float()
+            return kk, vv
+
+        total_budget = 100.0
+        per_step = max(1.0, total_budget / max(1, args.steps + args.warmup))
+        vals = []
+        for step in range(args.warmup + args.steps):
+            s, tok, done = cpu_attention_sample(w, q_cpu, rows, per_step, order[step % B:] + order[:step % B])
+            if step >= args.warmup:
+                vals.append(s * w.total_tokens / tok)
+        est = float(np.mean(vals))
+        cores = torch.get_num_threads()
+        line = {"impl": "reference", "metric": METRIC, "value": est * 1e6, "unit": UNIT, "n_gpus": n,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": est * 1e3,
+                "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": est * 1e6, "unit": UNIT, "cores": cores, "kind": "port",
+                                 "sample": f"per step: as many whole requests as fit in {per_step:.1f} s of dense fp32 "
+                                           f"attention on the host, scaled to the workload by token count"},
+                "e2e": {"value": est * 1e6, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    # ------------------------------------------------------------------ our arm (GPU)
+    assert torch.cuda.is_available(), "bench.py needs a GPU"
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if n > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from pat_b200 import PrefixTreeCPP, prefix_attn_with_kvcache
+    from pat_b200 import _prefix_attn as P
+
+    gen = torch.Generator(device=dev).manual_seed(w.seed * 100 + rank)
+    q_host = (torch.randn(B, 1, hq, D, generator=torch.Generator().manual_seed(w.seed)) * 0.5).to(dt).pin_memory()
+    k_cache = torch.empty(w.num_pages, page, hk, D, dtype=dt, device=dev)
+    v_cache = torch.empty_like(k_cache)
+    step_pages = 4096
+    for lo in range(0, w.num_pages, step_pages):        # bounded temporaries
+        hi = min(w.num_pages, lo + step_pages)
+        k_cache[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
+        v_cache[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
+    q = q_host.to(dev)
+    out = torch.empty_like(q)
+    out_host = torch.empty(B, 1, hq, D, dtype=dt).pin_memory()
+
+    table = torch.from_numpy(w.padded_table())
+    t0 = time.perf_counter()
+    tree = PrefixTreeCPP(page)
+    tree.build_radix_tree(list(w.seq_lens), table)
+    tree.pack_schedule(None, w.group, hk)
+    t1 = time.perf_counter()
+    tree.kernel_info.to_gpu(dev)
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    work = tree.kernel_info.device_work(dev)
+    hdr = work.header
+
+    flush = None
+    if bytes_rank < 4 * 126e6:
+        flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def step(flags=0):
+        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if n > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, iters):
+        """Average device milliseconds of fn over iters launches (flushes excluded)."""
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        for a, b in evs:
+            if flush is not None:
+                flush.fill_(1)
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / iters
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    wall0 = time.time()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / args.steps
+    else:
+        ms = timed(step, args.steps)
+        barrier()
+    launches = P.last_launch_count() * args.steps
+    wall1 = time.time()
+
+    # per-kernel durations (each phase alone; same stream, CUDA events)
+    reps = max(3, min(10, args.steps))
+    k_ms = {}
+    if hdr.num_stream_items:
+        k_ms["stream_kernel"] = timed(lambda: step(2 | 4), reps)
+    if hdr.num_dense_items:
+        k_ms["dense_kernel"] = timed(lambda: step(1 | 4), reps)
+    k_ms["merge_kernel"] = timed(lambda: step(1 | 2), reps)
+    step()   # leave `out` complete
+
+    # end to end: host queries + work list in, output back, every step
+    blob_host = work._host
+    def e2e_step():
+        q.copy_(q_host, non_blocking=True)
+        work.blob.copy_(blob_host, non_blocking=True)
+        step()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tw0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    tw1 = time.perf_counter()
+    e2e_ms = max(e0.elapsed_time(e1), (tw1 - tw0) * 1e3) / args.steps
+    wall2 = time.time()
+    sampler.stop()
+
+    vals = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if n > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = vals.tolist()
+
+    if rank != 0:
+        if n > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    elt = 2
+    kv_bytes = lambda tokens: 2 * tokens * hk * D * elt
+    dominant = max((k for k in k_ms if k != "merge_kernel"), key=lambda k_: k_ms[k_], default="merge_kernel")
+    if dominant == "stream_kernel":
+        alg = kv_bytes(hdr.stream_unique_tokens)
+    elif dominant == "dense_kernel":
+        alg = kv_bytes(hdr.dense_unique_tokens)
+    else:
+        alg = hdr.num_entries * hq * (D + 1) * 4 + B * hq * D * elt
+    achieved = alg / (k_ms[dominant] * 1e-3) / 1e9
+    step_gbs = bytes_rank / (ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": ms * 1e3, "unit": UNIT, "n_gpus": n, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": config,
+        "clocks": sampler.summary(wall0, wall2),
+        "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
+                "h2d_bytes_per_step": int(q_host.numel() * elt + blob_host.numel() * 4),
+                "d2h_bytes_per_step": int(out_host.numel() * elt)},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "algorithmic_bytes_per_launch": alg, "kernel_ms": k_ms[dominant]},
+        "step_roofline": {"dedup_bytes_per_gpu": bytes_rank, "dedup_bytes_total": bytes_total,
+                          "achieved_gbs_per_gpu": step_gbs, "frac_of_measured_copy": step_gbs / peak,
+                          "frac_of_8tbs": step_gbs / 8000.0},
+        "kernels_ms": k_ms,
+        "work": {"stream_items": hdr.num_stream_items, "dense_items": hdr.num_dense_items,
+                 "entries": hdr.num_entries, "segments": hdr.num_segments,
+                 "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
+        "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},
+    }
+
+    if n == 1 and not args.no_cpu_baseline:
+        q_cpu = q_host.float()
+        rng = np.random.default_rng(0)
+        order = rng.permutation(B).tolist()
+
+        def rows(b):
+            L = w.seq_lens[b]
+            idx = torch.as_tensor(w.block_tables[b][:-(-L // page)], device=dev, dtype=torch.long)
+            kk = k_cache[idx].reshape(-1, hk, D)[:L].float().cpu()
+            vv = v_cache[idx].reshape(-1, hk, D)[:L].float().cpu()
+            return kk, vv
+
+        s, tok, done = cpu_attention_sample(w, q_cpu, rows, args.cpu_seconds, order)
+        est = s * w.total_tokens / tok
+        line["cpu_baseline"] = {"value": est * 1e6, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"{done} of {B} requests ({tok} of {w.total_tokens} context tokens), "
+                                          f"{s:.1f} s of dense fp32 attention, scaled by token count"}
+    print(json.dumps(line))
+    if n > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

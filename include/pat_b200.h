@@ -131,7 +131,11 @@ typedef struct pat_work_header {
     int32_t items_off, queries_off, pages_off, merge_indptr_off, merge_entries_off;
     int32_t blob_words, num_segments;
     int32_t max_page_id, reserved;
-    int64_t unique_tokens, stream_tokens, dense_tokens;
+    int64_t unique_tokens;          /* valid tokens summed over segments: every page counted once */
+    int64_t stream_tokens;          /* tokens read by streaming items (a segment counts once per row chunk) */
+    int64_t dense_tokens;           /* same for dense items */
+    int64_t stream_unique_tokens;   /* unique tokens of the segments the streaming kernel handles */
+    int64_t dense_unique_tokens;
 } pat_work_header;
 
 /* Returns NULL and sets *status on failure. num_cache_pages > 0 enables a range check of page ids. */
@@ -152,6 +156,7 @@ const int32_t* pat_work_blob(const pat_work* w, size_t* words);
  * pat_run_mha_fwd_splitkv_dispatch (csrc/pat_fwd_launch_template.h:52-98).
  * ------------------------------------------------------------------------- */
 enum { PAT_DTYPE_FP16 = 0, PAT_DTYPE_BF16 = 1 };
+enum { PAT_SKIP_STREAM = 1, PAT_SKIP_DENSE = 2, PAT_SKIP_MERGE = 4 };
 
 typedef struct pat_decode_args {
     /* tensors (device pointers), strides in elements, last dimension contiguous */
@@ -169,7 +174,8 @@ typedef struct pat_decode_args {
     int32_t dtype;        /* PAT_DTYPE_* */
     int64_t num_pages;
     float softmax_scale;
-    int32_t flags;        /* reserved, 0 */
+    int32_t flags;        /* diagnostics: PAT_SKIP_* bits leave phases out (the result is then
+                             incomplete; used to time one kernel at a time) */
     /* work list */
     const int32_t* work_blob;   /* device copy of pat_work_blob */
     pat_work_header work;       /* host copy of the header */

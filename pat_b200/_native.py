@@ -43,7 +43,8 @@ class WorkHeader(C.Structure):
                 ("merge_indptr_off", C.c_int32), ("merge_entries_off", C.c_int32),
                 ("blob_words", C.c_int32), ("num_segments", C.c_int32),
                 ("max_page_id", C.c_int32), ("reserved", C.c_int32),
-                ("unique_tokens", C.c_int64), ("stream_tokens", C.c_int64), ("dense_tokens", C.c_int64)]
+                ("unique_tokens", C.c_int64), ("stream_tokens", C.c_int64), ("dense_tokens", C.c_int64),
+                ("stream_unique_tokens", C.c_int64), ("dense_unique_tokens", C.c_int64)]
 
 
 class DecodeArgs(C.Structure):

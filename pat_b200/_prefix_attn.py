@@ -332,7 +332,7 @@ def _check_index(t: torch.Tensor, name: str, shape=None):
         _check(tuple(t.shape) == tuple(shape), f"{name} must have shape {tuple(shape)}")
 
 
-def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None, status=None):
+def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None, status=None, flags=0):
     lib = N.load()
     B, _, H, D = q.shape
     a = N.DecodeArgs()
@@ -347,6 +347,7 @@ def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None,
     a.dtype = _DTYPES[q.dtype]
     a.num_pages = k_cache.shape[0]
     a.softmax_scale = float(scale)
+    a.flags = int(flags)
     a.work_blob = work.blob.data_ptr()
     a.work = work.header
     need = lib.pat_b200_workspace_bytes(C.byref(work.header), H, D)
@@ -378,6 +379,7 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
     """
     lse_out = kwargs.pop("lse_out", None)
     status = kwargs.pop("_status", None)
+    flags = kwargs.pop("_flags", 0)
     names16 = ["q", "k_cache_paged", "v_cache_paged", "num_split_per_seq", "query_tables", "block_tables",
                "num_seqs_per_CTAs", "CTA_ranks", "kv_in_CTAs", "MNW", "max_split_per_seq", "max_seqs_in_CTA",
                "max_blocks_in_CTA", "softmax_scale", "out", "timing_"]
@@ -473,7 +475,7 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
             tag.work[key] = work
 
     with torch.cuda.device(q.device):
-        _run(q, k_cache, v_cache, work, scale, out, lse_out, status)
+        _run(q, k_cache, v_cache, work, scale, out, lse_out, status, flags)
 
 
 def last_launch_count() -> int:

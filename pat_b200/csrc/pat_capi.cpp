@@ -48,6 +48,8 @@ void copy_header(const pat::WorkHeader& h, pat_work_header* out) {
     out->max_page_id = h.max_page_id; out->reserved = 0;
     out->unique_tokens = h.unique_tokens; out->stream_tokens = h.stream_tokens;
     out->dense_tokens = h.dense_tokens;
+    out->stream_unique_tokens = h.stream_unique_tokens;
+    out->dense_unique_tokens = h.dense_unique_tokens;
 }
 
 }  // namespace

@@ -88,7 +88,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     p.status = a.status_word;
 
     int launches = 0;
-    if (a.work.num_stream_items > 0) {
+    if (a.work.num_stream_items > 0 && !(a.flags & PAT_SKIP_STREAM)) {
         static bool configured[kMaxDevices] = {};
         auto kern = stream_kernel<T, D>;
         constexpr int smem = stream_smem_bytes<D>();
@@ -104,7 +104,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         kern<<<static_cast<unsigned>(grid), kStreamWarps * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
-    if (a.work.num_dense_items > 0) {
+    if (a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE)) {
         static bool configured[kMaxDevices] = {};
         auto kern = dense_kernel<T, D>;
         constexpr int smem = dense_smem_bytes<D>();
@@ -120,7 +120,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         kern<<<static_cast<unsigned>(grid), (kDenseWarps + 1) * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
-    {
+    if (!(a.flags & PAT_SKIP_MERGE)) {
         MergeParams mp{};
         mp.part_o = part_o;
         mp.part_lse = part_lse;

@@ -182,8 +182,13 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
     for (const Segment& sg : segs) {
         unique_tokens += sg.tokens;
         const int nq = static_cast<int>(sg.queries.size());
-        if (is_dense(sg)) dense_cost += sg.tokens * ceil_div(nq, q_per_dense);
-        else stream_cost += sg.tokens * ceil_div(nq, q_per_stream);
+        if (is_dense(sg)) {
+            dense_cost += sg.tokens * ceil_div(nq, q_per_dense);
+            header_.dense_unique_tokens += sg.tokens;
+        } else {
+            stream_cost += sg.tokens * ceil_div(nq, q_per_stream);
+            header_.stream_unique_tokens += sg.tokens;
+        }
     }
     auto pick_chunk = [&](int64_t cost, int cmin, int cmax, int per_sm) {
         int64_t want = cost * kv_heads / std::max<int64_t>(1, static_cast<int64_t>(opt.num_sms) * per_sm);

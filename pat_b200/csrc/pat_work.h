@@ -81,6 +81,8 @@ struct WorkHeader {
     int64_t unique_tokens;      // sum of segment tokens (each page counted once)
     int64_t stream_tokens;      // tokens read by streaming items (x row chunks)
     int64_t dense_tokens;
+    int64_t stream_unique_tokens;
+    int64_t dense_unique_tokens;
 };
 
 class WorkList {

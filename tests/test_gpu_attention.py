@@ -1,0 +1,262 @@
+"""Parity of the CUDA path with the fp32 oracle (run with ``-m gpu`` on a B200).
+
+Tolerances are the ones the task states: bf16 atol = rtol = 2e-2, fp16 1e-2 against
+the fp32 reference, LSE within 1e-3.  Every call goes through the public op and
+therefore through the C ABI (``pat_b200_decode``)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+from oracle import attention_oracle as O
+from pat_b200 import KernelInfo, PrefixTree, PrefixTreeCPP, AsyncTree, prefix_attn_with_kvcache
+from pat_b200 import _prefix_attn as P
+from pat_b200.workloads import make_config, make_values, scaled_down, torch_dtype
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.bfloat16: 2e-2, torch.float16: 1e-2}
+
+
+def _padded(tables):
+    width = max(len(r) for r in tables)
+    t = torch.zeros(len(tables), width, dtype=torch.int32)
+    for i, r in enumerate(tables):
+        t[i, :len(r)] = torch.tensor(r, dtype=torch.int32)
+    return t
+
+
+def _values(n_pages, page, hq, hk, d, batch, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(batch, 1, hq, d, generator=g) * 0.5).to(dtype)
+    k = (torch.randn(n_pages, page, hk, d, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(n_pages, page, hk, d, generator=g) * 0.5).to(dtype)
+    return q, k, v
+
+
+def _run_tree(q, k, v, seq_lens, tables, page, hratio, hk, scale, semantics="cpp", cfg=None, mnws=None):
+    tree = PrefixTreeCPP(page, semantics)
+    if semantics == "cpp":
+        tree.build_radix_tree(list(seq_lens), _padded(tables))
+    else:
+        tree.build_radix_tree(list(seq_lens), [list(r) for r in tables])
+    tree.pack_schedule(mnws, hratio, hk)
+    P.set_default_config(cfg)
+    try:
+        tree.kernel_info.to_gpu(torch.device(DEV))
+        qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+        out = torch.full_like(qd, float("nan"))
+        lse = torch.full((q.shape[0], q.shape[2]), float("nan"), device=DEV)
+        status = torch.zeros(4, dtype=torch.int32, device=DEV)
+        prefix_attn_with_kvcache(qd, kd, vd, tree, scale, out, lse_out=lse, _status=status)
+        torch.cuda.synchronize()
+    finally:
+        P.set_default_config(None)
+    assert status[0].item() == 0, "a bounded wait gave up inside a kernel"
+    return out.float().cpu()[:, 0], lse.cpu(), tree
+
+
+def _assert_close(out, lse, ref_o, ref_l, dtype):
+    tol = TOL[dtype]
+    err = (out - ref_o).abs()
+    bound = tol + tol * ref_o.abs()
+    assert bool((err <= bound).all()), f"max |dO| = {err.max().item():.3e}"
+    lerr = (lse - ref_l).abs().max().item()
+    assert lerr <= 1e-3, f"max |dLSE| = {lerr:.3e}"
+
+
+CONFIGS = [
+    # (dtype, hq, hk, d, page)
+    (torch.bfloat16, 32, 8, 128, 16),
+    (torch.float16, 32, 4, 64, 16),
+    (torch.bfloat16, 8, 8, 128, 16),      # MHA, ratio 1
+    (torch.float16, 16, 8, 128, 32),      # ratio 2, 32-token pages
+    (torch.bfloat16, 16, 2, 64, 16),      # ratio 8, D = 64
+]
+
+
+@pytest.mark.parametrize("dtype,hq,hk,d,page", CONFIGS)
+@pytest.mark.parametrize("seed", [3, 6, 8, 11])
+def test_random_batches(dtype, hq, hk, d, page, seed, native_lib):
+    case = C.random_case(seed)
+    # rebuild the same structure on the requested page size
+    lens = [max(1, l * page // case.block_size - (l % 3)) for l in case.seq_lens]
+    tables = [r[:max(1, -(-lens[i] // page))] for i, r in enumerate(case.tables)]
+    lens = [min(l, len(t) * page) for l, t in zip(lens, tables)]
+    # a request must own its last page unless it fills it
+    fresh = max(max(r) for r in tables) + 1
+    for i, (l, t) in enumerate(zip(lens, tables)):
+        if l % page:
+            t[-1] = fresh
+            fresh += 1
+    q, k, v = _values(fresh, page, hq, hk, d, len(lens), dtype, seed)
+    scale = 1.0 / math.sqrt(d)
+    out, lse, _ = _run_tree(q, k, v, lens, tables, page, hq // hk, hk, scale)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, lens, tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
+
+
+@pytest.mark.parametrize("cfg", [0, 1, 2])
+def test_benchmark_configs_full(cfg, native_lib):
+    w = make_config(cfg)
+    q, k, v = make_values(w)
+    dtype = torch_dtype(w.dtype)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    out, lse, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
+
+
+@pytest.mark.parametrize("cfg,sample", [(3, 24), (4, 12)])
+def test_benchmark_configs_full_sampled(cfg, sample, native_lib):
+    """Full-size workloads: the oracle checks a seeded sample of requests, and the result
+    must not depend on how the work was cut (decomposition invariance)."""
+    w = make_config(cfg)
+    q, k, v = make_values(w)
+    dtype = torch_dtype(w.dtype)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    out, lse, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale)
+    rng = np.random.default_rng(cfg)
+    picks = sorted(set(rng.integers(0, w.batch, sample).tolist()) | {0, w.batch - 1})
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale, requests=picks)
+    _assert_close(out[picks], lse[picks], ref_o[:, 0], ref_l, dtype)
+    # other cuts of the same work: streaming kernel only, and tiny chunks
+    alt1, lse1, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale,
+                              cfg=P.WorkConfig(disable_dense=1))
+    alt2, lse2, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale,
+                              semantics="py", cfg=P.WorkConfig(chunk_tokens_max=512, dense_chunk_tokens_max=512))
+    tol = TOL[dtype]
+    assert (out - alt1).abs().max().item() <= tol
+    assert (out - alt2).abs().max().item() <= tol
+    assert (lse - lse1).abs().max().item() <= 1e-3
+    assert (lse - lse2).abs().max().item() <= 1e-3
+
+
+@pytest.mark.parametrize("cfg,factor", [(3, 4), (4, 32)])
+def test_scaled_configs_all_requests(cfg, factor, native_lib):
+    w = scaled_down(cfg, factor)
+    q, k, v = make_values(w)
+    dtype = torch_dtype(w.dtype)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    out, lse, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
+
+
+@pytest.mark.parametrize("opts", [dict(disable_dense=1), dict(dense_min_rows=64),
+                                  dict(chunk_tokens_min=16, chunk_tokens_max=64, dense_chunk_tokens_max=64),
+                                  dict(items_per_sm=64)])
+def test_work_cuts_agree_with_oracle(opts, native_lib):
+    w = scaled_down(1, 4)
+    q, k, v = make_values(w)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    out, lse, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale,
+                            cfg=P.WorkConfig(**opts))
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, torch.bfloat16)
+
+
+def test_sixteen_argument_form_with_python_scheduler(native_lib):
+    """The call the reference's kernel benchmark makes (benchmark/benchmark_kernel.py:234-265)."""
+    w = make_config(0)
+    q, k, v = make_values(w)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    tree = PrefixTree(w.page_size)
+    tree.build_radix_tree(list(w.seq_lens), [list(r) for r in w.block_tables])
+    ki: KernelInfo = tree.pack_schedule(MNWs=None, HRatio=w.group, kvHead=w.num_kv_heads, use_compute_model=False)
+    ki.to_tensor(device=DEV)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out = torch.empty_like(qd)
+    lse = torch.empty(w.batch, w.num_q_heads, device=DEV)
+
+    def call(o):
+        prefix_attn_with_kvcache(qd, kd, vd, ki.num_split_per_seq, ki.q_tables, ki.block_tables,
+                                 ki.num_seqs_per_CTAs, ki.CTA_ranks, ki.kv_in_CTAs, ki.MNWs, ki.max_split_per_seq,
+                                 ki.max_seqs_in_CTA, ki.max_blocks_in_CTA, scale, o, None, lse_out=lse)
+    call(out)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(out.float().cpu()[:, 0], lse.cpu(), ref_o[:, 0], ref_l, torch.bfloat16)
+    # bare tensors without the attached host plan (one D2H read-back) give the same result
+    bare = [t.clone() for t in (ki.num_split_per_seq,)]
+    out2 = torch.empty_like(qd)
+    prefix_attn_with_kvcache(qd, kd, vd, bare[0], [t.clone() for t in ki.q_tables],
+                             [t.clone() for t in ki.block_tables], [t.clone() for t in ki.num_seqs_per_CTAs],
+                             [t.clone() for t in ki.CTA_ranks], [t.clone() for t in ki.kv_in_CTAs], ki.MNWs,
+                             ki.max_split_per_seq, ki.max_seqs_in_CTA, ki.max_blocks_in_CTA, scale, out2)
+    assert torch.equal(out, out2)
+
+
+def test_async_tree_and_strided_views_like_the_serving_backend(native_lib):
+    """plugin/vllm/attention/backends/prefix_attn.py:330-338, 806-807, 908-915: AsyncTree from a
+    padded CPU table, caches as the two halves of one tensor, q / out as unsqueezed views."""
+    w = scaled_down(2, 4)
+    q, k, v = make_values(w)
+    dtype = torch_dtype(w.dtype)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    kv = torch.stack([k, v]).to(DEV)                      # [2, pages, page, hk, d]
+    key_cache, value_cache = kv[0], kv[1]
+    decode_query = q[:, 0].to(DEV)                        # [B, H, D]
+    decode_output = torch.empty_like(decode_query)
+    at = AsyncTree(block_size=w.page_size, seq_lens=list(w.seq_lens), table=_padded(w.block_tables), MNWs=None,
+                   HRatio=w.group, kvHead=w.num_kv_heads, device=torch.device(DEV))
+    tree = at.tree
+    lse = torch.empty(w.batch, w.num_q_heads, device=DEV)
+    prefix_attn_with_kvcache(q=decode_query.unsqueeze(1), k_cache_paged=key_cache, v_cache_paged=value_cache,
+                             tree=tree, softmax_scale=scale, out=decode_output.unsqueeze(1), lse_out=lse)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(decode_output.float().cpu(), lse.cpu(), ref_o[:, 0], ref_l, dtype)
+
+
+def test_garbage_beyond_the_valid_tokens_is_ignored(native_lib):
+    """Cache rows past a request's length may hold anything (NaN included)."""
+    page, hq, hk, d = 16, 16, 2, 128
+    lens = [5, 37, 16, 1, 250]
+    tables = [[0], [1, 2, 3], [4], [5], list(range(6, 22))]
+    q, k, v = _values(22, page, hq, hk, d, len(lens), torch.bfloat16, 5)
+    kk, vv = k.clone(), v.clone()
+    for L, t in zip(lens, tables):
+        if L % page:
+            kk[t[-1], L % page:] = float("nan")
+            vv[t[-1], L % page:] = float("inf")
+    scale = 1.0 / math.sqrt(d)
+    out, lse, _ = _run_tree(q, kk, vv, lens, tables, page, hq // hk, hk, scale)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, lens, tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, torch.bfloat16)
+
+
+def test_identical_requests_share_every_page(native_lib):
+    page, hq, hk, d = 16, 32, 4, 128
+    lens = [700] * 40
+    tables = [list(range(44))] * 40
+    q, k, v = _values(44, page, hq, hk, d, 40, torch.float16, 9)
+    scale = 1.0 / math.sqrt(d)
+    out, lse, tree = _run_tree(q, k, v, lens, tables, page, hq // hk, hk, scale)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, lens, tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, torch.float16)
+    work = tree.kernel_info.device_work(torch.device(DEV))
+    assert work.header.unique_tokens == 700 and work.header.num_dense_items > 0
+
+
+def test_reference_error_behaviour_on_device(native_lib):
+    w = scaled_down(0, 8)
+    q, k, v = make_values(w, device=DEV)
+    tree = PrefixTreeCPP(w.page_size)
+    tree.build_radix_tree(list(w.seq_lens), _padded(w.block_tables))
+    tree.pack_schedule(None, w.group, w.num_kv_heads)
+    out = torch.empty_like(q)
+    with pytest.raises(RuntimeError, match="must be on CUDA"):        # plan not moved to the GPU
+        prefix_attn_with_kvcache(q, k, v, tree, 0.1, out)
+    tree.kernel_info.to_gpu(DEV)
+    with pytest.raises(RuntimeError, match="same dtype"):
+        prefix_attn_with_kvcache(q, k.half(), v, tree, 0.1, out)
+    with pytest.raises(RuntimeError, match="fp16 and bf16"):
+        prefix_attn_with_kvcache(q.float(), k.float(), v.float(), tree, 0.1, out.float())
+    with pytest.raises(RuntimeError, match="head_size"):
+        prefix_attn_with_kvcache(q[..., :32].contiguous(), k[..., :32].contiguous(), v[..., :32].contiguous(),
+                                 tree, 0.1, out[..., :32].contiguous())
+    prefix_attn_with_kvcache(q, k, v, tree, 0.1, out)                  # and the good call still works
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert P.last_launch_count() >= 2
