@@ -47,6 +47,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scale-down", type=int, default=1,
+                    help="divide every segment length by this factor (profiling captures on a small case)")
     return ap.parse_args()
 
 
@@ -143,8 +145,8 @@ def main():
             sys.exit(2)
     n = world
 
-    from pat_b200.workloads import make_config, torch_dtype
-    w = make_config(args.config)
+    from pat_b200.workloads import make_config, scaled_down, torch_dtype
+    w = make_config(args.config) if args.scale_down <= 1 else scaled_down(args.config, args.scale_down)
     if w.num_kv_heads % n != 0:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "unavailable": f"{w.num_kv_heads} KV heads do not shard over {n} GPUs"}))
