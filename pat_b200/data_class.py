@@ -206,13 +206,16 @@ class KernelInfo:
         if self.sort_index is not None and not isinstance(self.sort_index, torch.Tensor):
             self.sort_index = as_i32(self.sort_index)
 
-        if not isinstance(self.num_seqs_per_CTAs, torch.Tensor):
+        def listed(seq):   # a list that still holds Python lists (not yet converted)
+            return not isinstance(seq, torch.Tensor) and not all(isinstance(t, torch.Tensor) for t in seq)
+
+        if listed(self.num_seqs_per_CTAs):
             self.num_seqs_per_CTAs = [as_i32(x) for x in self.num_seqs_per_CTAs]
         if not all(isinstance(t, torch.Tensor) for t in self.q_tables):
             self.q_tables = [as_i32(_pad_rows(t)) for t in self.q_tables]
-        if not isinstance(self.CTA_ranks, torch.Tensor):
+        if listed(self.CTA_ranks):
             self.CTA_ranks = [as_i32(x) for x in self.CTA_ranks]
-        if not isinstance(self.kv_in_CTAs, torch.Tensor):
+        if listed(self.kv_in_CTAs):
             self.kv_in_CTAs = [as_i32(x) for x in self.kv_in_CTAs]
         if not all(isinstance(t, torch.Tensor) for t in self.block_tables):
             self.block_tables = [as_i32(_pad_rows(t)) for t in self.block_tables]

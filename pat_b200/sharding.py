@@ -1,0 +1,68 @@
+"""KV-head sharding across the GPUs of one node.
+
+Every KV head (with its group of query heads) is an independent slice of the decode-attention
+problem: the reference's own grid puts the KV head on ``blockIdx.y``
+(``csrc/pat_fwd_launch_template.h:37``) and a tensor-parallel vLLM hands the backend per-rank
+head counts (``plugin/vllm/attention/backends/prefix_attn.py:617-618``).  Rank ``r`` of ``n``
+owns KV heads ``[r*Hkv/n, (r+1)*Hkv/n)`` and the matching query heads; block tables and plans
+are replicated host work (packed with ``kvHead = Hkv/n``).  No kernel reads another GPU's
+memory and no collective sits on the data path; ``all_gather_heads`` is the one optional
+collective, for callers that want the full ``[batch, 1, H, D]`` output on every rank (in a
+tensor-parallel model the row-parallel output projection consumes the shard locally instead).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+
+def kv_head_range(num_kv_heads: int, world: int, rank: int) -> Tuple[int, int]:
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    if num_kv_heads % world != 0:
+        raise ValueError(f"{num_kv_heads} KV heads cannot be split evenly over {world} ranks")
+    per = num_kv_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_views(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, world: int, rank: int):
+    """Views (no copies) of this rank's heads: ``q [B,1,H/n,D]``, caches ``[pages, page, Hkv/n, D]``.
+    The op honours the strides, so the views can be passed as they are."""
+    hk = k_cache.shape[2]
+    group = q.shape[2] // hk
+    lo, hi = kv_head_range(hk, world, rank)
+    return q[:, :, lo * group: hi * group], k_cache[:, :, lo:hi], v_cache[:, :, lo:hi]
+
+
+def all_gather_heads(out_shard: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """Concatenate the ranks' ``[B, 1, H/n, D]`` outputs along the head axis (rank order)."""
+    if world == 1:
+        return out_shard
+    import torch.distributed as dist
+    parts = [torch.empty_like(out_shard) for _ in range(world)]
+    dist.all_gather(parts, out_shard.contiguous(), group=group)
+    return torch.cat(parts, dim=2)
+
+
+class ShardedDecode:
+    """One rank's share of a decode step: a plan packed for ``Hkv/n`` KV heads plus the op call."""
+
+    def __init__(self, block_size: int, seq_lens, block_table: torch.Tensor, num_q_heads: int,
+                 num_kv_heads: int, world: int, rank: int, device, semantics: str = "cpp"):
+        from ._prefix_attn import PrefixTreeCPP
+        self.world, self.rank = world, rank
+        self.lo, self.hi = kv_head_range(num_kv_heads, world, rank)
+        self.group = num_q_heads // num_kv_heads
+        self.tree = PrefixTreeCPP(block_size, semantics)
+        self.tree.build_radix_tree(seq_lens, block_table)
+        self.tree.pack_schedule(None, self.group, self.hi - self.lo)
+        self.tree.kernel_info.to_gpu(device)
+
+    def __call__(self, q_shard, k_shard, v_shard, softmax_scale: float, out_shard: Optional[torch.Tensor] = None,
+                 lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from ._prefix_attn import prefix_attn_with_kvcache
+        if out_shard is None:
+            out_shard = torch.empty_like(q_shard)
+        prefix_attn_with_kvcache(q_shard, k_shard, v_shard, self.tree, softmax_scale, out_shard, lse_out=lse_out)
+        return out_shard
