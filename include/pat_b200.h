@@ -192,6 +192,27 @@ int pat_b200_decode(const pat_decode_args* args, void* stream);
 /* Number of kernels the last successful pat_b200_decode call on this thread launched. */
 int pat_b200_last_launch_count(void);
 
+/* Decode for callers that cannot allocate device memory - a serving engine that has handed the
+ * whole GPU to its own memory pool, or a decode loop where a device allocation could block,
+ * synchronise or fail.  (It has no counterpart in the reference, which allocates its partial
+ * buffers inside every call, csrc/api.h:217-238.)
+ *
+ * Same arguments and result as pat_b200_decode, except that args->workspace and
+ * args->workspace_bytes are ignored: the per-(item, query) partial results go to a fixed array
+ * of PAT_B200_STATIC_SCRATCH_BYTES that is part of the library's device image (each GPU that
+ * loads the library holds that much memory until the process exits).  A work list that needs
+ * more (pat_b200_workspace_bytes(...) > PAT_B200_STATIC_SCRATCH_BYTES) is refused with
+ * PAT_ERR_TOO_LARGE and nothing is launched.  The call itself allocates nothing.
+ *
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside of any stream capture.
+ * All calls on a device share the one array and it keeps whatever the previous call left there.
+ * Nothing in it has to start at zero - every slot the merge reads is written earlier in the same
+ * call - but two calls whose kernels overlap on the GPU (different streams, or different host
+ * threads) would overwrite each other's partial results: run them one after the other. */
+#define PAT_B200_STATIC_SCRATCH_BYTES (32u << 20)
+int pat_b200_decode_static_scratch(const pat_decode_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -90,7 +90,9 @@ SIGNATURES = {
     "pat_b200_workspace_bytes": (C.c_size_t, [C.POINTER(WorkHeader), C.c_int, C.c_int]),
     "pat_b200_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "pat_b200_last_launch_count": (C.c_int, []),
+    "pat_b200_decode_static_scratch": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
 }
+STATIC_SCRATCH_BYTES = 32 << 20
 
 _lib = None
 _lock = threading.Lock()

@@ -10,6 +10,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 
@@ -202,3 +203,37 @@ int pat_b200_decode(const pat_decode_args* args, void* stream_handle) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------
+// Decode without any allocation: the partial results live in a fixed device array.
+// ------------------------------------------------------------------------------
+// Scratch for pat_b200_decode_static_scratch.  It is part of the module image, so every GPU
+// that loads this library holds PAT_B200_STATIC_SCRATCH_BYTES of it until the process exits.
+static __device__ __align__(256) unsigned char g_pat_static_scratch[PAT_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_pat_static_scratch per device.  In host code the array's name is only a
+// handle for the runtime, never a device pointer: the address has to be asked for, once per
+// device, while that device is current.
+std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
+}  // namespace
+
+extern "C" int pat_b200_decode_static_scratch(const pat_decode_args* args, void* stream_handle) {
+    if (!args) return PAT_ERR_BAD_ARGUMENT;
+    if (args->num_q_heads <= 0 || args->head_dim <= 0 || args->work.num_entries < 0) return PAT_ERR_BAD_ARGUMENT;
+    const size_t need = pat_b200_workspace_bytes(&args->work, args->num_q_heads, args->head_dim);
+    if (need > static_cast<size_t>(PAT_B200_STATIC_SCRATCH_BYTES)) return PAT_ERR_TOO_LARGE;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return PAT_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return PAT_ERR_UNSUPPORTED;
+    void* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!ptr) {
+        // first call on this device (which is current): resolve the symbol's device address
+        if (cudaGetSymbolAddress(&ptr, g_pat_static_scratch) != cudaSuccess || !ptr) return PAT_ERR_CUDA;
+        g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
+    }
+    pat_decode_args local = *args;
+    local.workspace = ptr;
+    local.workspace_bytes = PAT_B200_STATIC_SCRATCH_BYTES;
+    return pat_b200_decode(&local, stream_handle);
+}
