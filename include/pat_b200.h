@@ -156,7 +156,8 @@ const int32_t* pat_work_blob(const pat_work* w, size_t* words);
  * pat_run_mha_fwd_splitkv_dispatch (csrc/pat_fwd_launch_template.h:52-98).
  * ------------------------------------------------------------------------- */
 enum { PAT_DTYPE_FP16 = 0, PAT_DTYPE_BF16 = 1 };
-enum { PAT_SKIP_STREAM = 1, PAT_SKIP_DENSE = 2, PAT_SKIP_MERGE = 4 };
+enum { PAT_SKIP_STREAM = 1, PAT_SKIP_DENSE = 2, PAT_SKIP_MERGE = 4,
+       PAT_DENSE_MMA_SYNC = 8 /* run the dense tiles on the legacy mma.sync kernel instead of tcgen05 */ };
 
 typedef struct pat_decode_args {
     /* tensors (device pointers), strides in elements, last dimension contiguous */

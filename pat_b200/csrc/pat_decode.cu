@@ -14,6 +14,7 @@
 #include <cmath>
 #include <cstdio>
 
+#include "pat_dense_tc.cuh"
 #include "pat_kernels.cuh"
 
 namespace {
@@ -105,7 +106,24 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         kern<<<static_cast<unsigned>(grid), kStreamWarps * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
-    if (a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE)) {
+    if (a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE) && !(a.flags & PAT_DENSE_MMA_SYNC)) {
+        // dense tiles on tcgen05 / TMEM
+        static bool configured[kMaxDevices] = {};
+        auto kern = dense_tc_kernel<T, D>;
+        constexpr int smem = TcSmem<D>::kRequest;
+        if (!configured[dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return PAT_ERR_CUDA;
+            configured[dev] = true;
+        }
+        p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
+        p.num_items = a.work.num_dense_items;
+        const long long grid = static_cast<long long>(p.num_items) * a.num_kv_heads;
+        if (grid > 0x7fffffffLL) return PAT_ERR_TOO_LARGE;
+        kern<<<static_cast<unsigned>(grid), kTcThreads, smem, stream>>>(p, kmap, vmap);
+        ++launches;
+    } else if (a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE)) {
+        // the same tiles on the legacy mma.sync path (kept for comparison)
         static bool configured[kMaxDevices] = {};
         auto kern = dense_kernel<T, D>;
         constexpr int smem = dense_smem_bytes<D>();

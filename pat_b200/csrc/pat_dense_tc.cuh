@@ -1,0 +1,394 @@
+// Dense-tile attention on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// One CTA = one dense work item (up to 128 query rows that share a KV chunk) x one KV head.
+// Replaces the reference's M=64 mma.sync tile (csrc/pat_fwd_kernel.h:25-299,
+// csrc/kernel_traits.h:45-123) for segments that many queries share.
+//
+//   warps 0-3 (128 threads): thread r owns query row r = TMEM lane r.  Per 64-token tile it
+//            reads its row of S = Q K^T from TMEM (tcgen05.ld), does the online softmax with
+//            no cross-thread traffic, and writes P (bf16/fp16) to shared memory.
+//   thread 0 additionally issues the MMAs: S_j = Q K_j^T (M128 N64 K16 x D/16) one tile
+//            ahead, O += P_j V_j (M128 N=D K16 x 4) after the tile's softmax; completion is
+//            tracked with tcgen05.commit on mbarriers.
+//   warp 4 / warp 5: TMA producers for K and for V, 2 stages of 64 tokens each (boxes of
+//            16 tokens x 64 elements, 128-byte swizzle - the layout the UMMA shared-memory
+//            descriptors below describe).  A K stage is released as soon as its S = Q K^T has
+//            completed and a V stage when its P V has, so both run about two tiles ahead.
+//
+// TMEM: 256 columns per CTA: S double-buffered (2 x 64 fp32 columns) + O (D columns).
+// Shared memory: 112.25 KB per CTA, so two CTAs share an SM (and its 512 TMEM columns); one
+// CTA's softmax overlaps the other's MMAs.
+// The running maximum is only raised when a tile exceeds it by more than 2^8 (the exponent
+// offset cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
+// Every mbarrier wait is bounded; a wait that gives up records a code in the status word,
+// later waits are skipped and the CTA still frees its TMEM before it returns.
+#pragma once
+
+#include "pat_kernels.cuh"
+
+namespace pat {
+
+constexpr int kTcTile = 64;                 // tokens per tile
+constexpr int kTcStages = 2;
+constexpr int kTcThreads = 192;
+constexpr int kTcTmemCols = 256;
+constexpr float kTcLazyLog2 = 8.0f;
+
+template <int D> struct TcSmem {
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kQBytes = kBoxes * 128 * 128;          // [box][128 rows][128 B]
+    static constexpr int kKBytes = kBoxes * kTcTile * 128;      // [box][64 tokens][128 B]
+    static constexpr int kVBytes = kKBytes;
+    static constexpr int kPBytes = 128 * 128;                   // [128 rows][64 tokens x 2 B]
+    static constexpr int kQOff = 0;
+    static constexpr int kKOff = kQOff + kQBytes;
+    static constexpr int kVOff = kKOff + kTcStages * kKBytes;
+    static constexpr int kPOff = kVOff + kTcStages * kVBytes;
+    static constexpr int kBarOff = kPOff + kPBytes;             // 11 mbarriers + tmem base word
+    static constexpr int kUsed = kBarOff + 128;
+    // Fixed request (also for D = 64) so that exactly two CTAs fit on an SM: a third one would
+    // only wait for TMEM columns.
+    static constexpr int kRequest = 114944;
+    static_assert(kUsed <= kRequest, "shared memory layout exceeds the per-CTA budget");
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+#define PAT_TMEM_LIST64(p) \
+    p(0) p(1) p(2) p(3) p(4) p(5) p(6) p(7) p(8) p(9) p(10) p(11) p(12) p(13) p(14) p(15) \
+    p(16) p(17) p(18) p(19) p(20) p(21) p(22) p(23) p(24) p(25) p(26) p(27) p(28) p(29) p(30) p(31) \
+    p(32) p(33) p(34) p(35) p(36) p(37) p(38) p(39) p(40) p(41) p(42) p(43) p(44) p(45) p(46) p(47) \
+    p(48) p(49) p(50) p(51) p(52) p(53) p(54) p(55) p(56) p(57) p(58) p(59) p(60) p(61) p(62) p(63)
+
+// 64 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[64]) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x64.b32 [%64], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+          "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]),
+          "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]),
+          "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]),
+          "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63]),
+          "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---- UMMA descriptors -------------------------------------------------------------
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4),
+// descriptor version 1, 128-byte swizzle (layout type 2).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu) |
+           (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// K-major operand (rows of 128 B = 64 elements, groups of 8 rows 1024 B apart): the leading
+// offset is unused by the swizzled K-major layouts and set to 16 B.
+__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr) { return umma_desc(smem_addr, 16, 1024); }
+// MN-major operand: 64 elements along MN per 128-B row, next 64 along MN `mn_stride` bytes on,
+// groups of 8 K-rows 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t smem_addr, uint32_t mn_stride) {
+    return umma_desc(smem_addr, mn_stride, 1024);
+}
+// Instruction descriptor of kind::f16: fp32 accumulate, A/B format (0 = f16, 1 = bf16),
+// A K-major, B K-major or MN-major, N >> 3 at bit 17, M >> 4 at bit 24.
+template <typename T> __device__ __forceinline__ uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+    const uint32_t fmt = sizeof(T) == 2 && Elt<T>::kTma == CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kTcThreads)
+dense_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    using L = TcSmem<D>;
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    const uint32_t base = smem_u32(tc_smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((base & 1023u) != 0) {          // the swizzled layouts need a 1024-byte aligned window
+        if (tid == 0 && p.status) atomicExch(p.status, 10);
+        return;
+    }
+    const uint32_t sQ = base + L::kQOff, sK = base + L::kKOff, sV = base + L::kVOff, sP = base + L::kPOff;
+    const uint32_t bars = base + L::kBarOff;
+    const uint32_t bar_full_k = bars, bar_full_v = bars + 16, bar_empty_k = bars + 32, bar_empty_v = bars + 48,
+                   bar_s = bars + 64, bar_o = bars + 80;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 96);
+
+    const int item_idx = blockIdx.x / p.kv_heads;
+    const int kvh = blockIdx.x - item_idx * p.kv_heads;
+    const int32_t* it = p.items + static_cast<size_t>(item_idx) * 8;
+    const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
+              entry_base = __ldg(it + 4);
+    const int rows_valid = nq * p.hratio;
+    const int n_sub = (kv_len + 15) >> 4;
+    const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
+
+    // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 104);
+    if (tid == 0) *poisoned = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
+    __syncthreads();
+    if (*poisoned) return;
+
+    if (tid == 0) {
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        for (int i = 0; i < 11; ++i) mbar_init(bars + 8 * i, 1);   // full_k/v[2] empty_k/v[2] s[2] o
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTcTmemCols);
+
+    // ---- Q rows into the swizzled K-major layout (thread r = row r) ------------------
+    if (tid < 128) {
+        const int r = tid;
+        const uint4* src = nullptr;
+        if (r < rows_valid) {
+            const int qi = r / p.hratio, g = r - qi * p.hratio;
+            const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
+                         static_cast<int64_t>(kvh * p.hratio + g) * p.q_head_stride;
+            src = reinterpret_cast<const uint4*>(q);
+        }
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const uint4 v = src ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+            const uint32_t dst = sQ + (c >> 3) * (128 * 128) + swz128(r, c & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+        fence_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_per_page = p.page_size >> 4;
+    const int32_t* item_pages = p.pages + page_off;
+
+    if (warp >= 4) {
+        // ---- TMA producers: warp 4 streams K, warp 5 streams V -----------------------------
+        const bool is_k = warp == 4;
+        const CUtensorMap* map = is_k ? &kmap : &vmap;
+        const uint32_t stage0 = is_k ? sK : sV;
+        const uint32_t full = is_k ? bar_full_k : bar_full_v;
+        const uint32_t empty = is_k ? bar_empty_k : bar_empty_v;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            if (j >= kTcStages && ok) ok = mbar_wait(empty + 8 * s, ((j >> 1) - 1) & 1);
+            if (!ok) break;
+            const int subs = min(4, n_sub - j * 4);
+            if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
+            __syncwarp();
+            if (lane < subs) {
+                const int t = j * 4 + lane;
+                const int page = __ldg(item_pages + t / tiles_per_page);
+                const int row0 = (t % tiles_per_page) << 4;
+#pragma unroll
+                for (int b = 0; b < L::kBoxes; ++b)
+                    tma_load_4d(stage0 + s * L::kKBytes + b * (kTcTile * 128) + lane * 2048, map, full + 8 * s,
+                                b * 64, kvh, row0, page);
+            }
+            __syncwarp();
+        }
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
+        return;
+    }
+
+    // ---- softmax threads (thread 0 also issues the MMAs) ------------------------------------
+    const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
+    const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t tmem_o = tmem_base + 2 * kTcTile;
+    const float c = p.scale_log2;
+    bool ok = true;
+
+    auto issue_qk = [&](int j) {       // thread 0: S[j & 1] = Q K_j^T
+        const int s = j & 1;
+        if (ok) ok = mbar_wait(bar_full_k + 8 * s, (j >> 1) & 1);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const uint64_t a = umma_desc_kmajor(sQ + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
+            const uint64_t b = umma_desc_kmajor(sK + s * L::kKBytes + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
+            tc_mma(tmem_base + s * kTcTile, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(bar_s + 8 * s);
+        tc_commit(bar_empty_k + 8 * s);      // the K stage is free once this product has completed
+    };
+
+    if (tid == 0) issue_qk(0);
+    float m_used = -INFINITY, l = 0.f;
+    for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (tid == 0 && j + 1 < n_tiles) issue_qk(j + 1);
+        if (ok) ok = mbar_wait(bar_s + 8 * s, (j >> 1) & 1);
+        tc_fence_after();
+        float sc[64];
+        tmem_ld64(lane_addr + s * kTcTile, sc);
+        const int valid = min(kTcTile, kv_len - j * kTcTile);
+        if (valid < kTcTile) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+                if (i >= valid) sc[i] = -INFINITY;
+        }
+        float mx = sc[0];
+#pragma unroll
+        for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sc[i]);
+
+        // the previous PV must be done before P is overwritten or O is rescaled
+        if (j > 0 && ok) ok = mbar_wait(bar_o, (j - 1) & 1);
+        tc_fence_after();
+        const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
+        if (j > 0 && __any_sync(kFullMask, raise)) {
+            const float alpha = raise ? fast_exp2((m_used - mx) * c) : 1.f;
+            l *= alpha;
+#pragma unroll 1
+            for (int h = 0; h < D / 64; ++h) {
+                float ov[64];
+                tmem_ld64(lane_addr + 2 * kTcTile + h * 64, ov);
+#pragma unroll
+                for (int i = 0; i < 64; ++i) ov[i] *= alpha;
+                tmem_st64(lane_addr + 2 * kTcTile + h * 64, ov);
+            }
+        }
+        if (raise) m_used = mx;
+        const float off = m_used * c;
+        float sum = 0.f;
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
+            const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
+            sum += p0 + p1;
+            packed[i] = Elt<T>::pack(p0, p1);
+        }
+        l += sum;
+        {   // row tid of P: 8 chunks of 16 B, swizzled like a [128 x 128 B] K-major tile
+            const int r = tid;
+#pragma unroll
+            for (int k8 = 0; k8 < 8; ++k8) {
+                const uint32_t dst = sP + swz128(r, k8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * k8]), "r"(packed[4 * k8 + 1]),
+                             "r"(packed[4 * k8 + 2]), "r"(packed[4 * k8 + 3]) : "memory");
+            }
+        }
+        if (valid < kTcTile) {
+            // V rows past the valid tokens may hold anything (stale tiles, never written pages):
+            // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
+            if (ok) ok = mbar_wait(bar_full_v + 8 * s, (j >> 1) & 1);
+            const int rows = kTcTile - valid;
+            const int chunks = rows * 8 * L::kBoxes;
+            for (int i = tid; i < chunks; i += 128) {
+                const int b = i / (rows * 8);
+                const int rem = i - b * rows * 8;
+                const int row = valid + (rem >> 3);
+                const uint32_t dst = sV + s * L::kVBytes + b * (kTcTile * 128) + row * 128 + ((rem & 7) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        named_bar_sync(1, 128);
+        if (tid == 0) {
+            if (ok) ok = mbar_wait(bar_full_v + 8 * s, (j >> 1) & 1);
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < kTcTile / 16; ++ks) {
+                const uint64_t a = umma_desc_kmajor(sP + ks * 32);
+                const uint64_t b = umma_desc_mnmajor(sV + s * L::kVBytes + ks * 2048, kTcTile * 128);
+                tc_mma(tmem_o, a, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+            }
+            tc_commit(bar_o);
+            tc_commit(bar_empty_v + 8 * s);
+        }
+    }
+
+    // ---- epilogue: O / l -> fp32 partial, LSE -------------------------------------------------
+    if (ok) ok = mbar_wait(bar_o, (n_tiles - 1) & 1);
+    tc_fence_after();
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
+    {
+        const int r = tid;
+        const bool store = ok && r < rows_valid;
+        size_t slot = 0;
+        if (r < rows_valid) {
+            const int qi = r / p.hratio, g = r - qi * p.hratio;
+            slot = static_cast<size_t>(entry_base + qi) * p.num_q_heads + kvh * p.hratio + g;
+        }
+        const float inv = 1.f / l;
+#pragma unroll 1
+        for (int h = 0; h < D / 64; ++h) {
+            float ov[64];
+            tmem_ld64(lane_addr + 2 * kTcTile + h * 64, ov);
+            if (store) {
+                float4* dst = reinterpret_cast<float4*>(p.part_o + slot * D + h * 64);
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+            }
+        }
+        if (store) p.part_lse[slot] = m_used * p.scale + logf(l);
+    }
+    tc_fence_before();
+    named_bar_sync(1, 128);
+    if (warp == 0) tmem_dealloc(tmem_base, kTcTmemCols);
+}
+
+}  // namespace pat

@@ -40,10 +40,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within kMaxPolls polls.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false if the phase did not complete within about kMaxWaitNs (or kMaxPolls
+// polls, whichever comes first).  The clock is only read every 256 polls.
+constexpr uint64_t kMaxWaitNs = 1000ull * 1000ull * 1000ull;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kMaxPolls; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t i = 1; i < kMaxPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 0 && global_timer_ns() - start > kMaxWaitNs) return false;
+    }
     return false;
 }
 

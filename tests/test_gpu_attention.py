@@ -36,7 +36,7 @@ def _values(n_pages, page, hq, hk, d, batch, dtype, seed):
     return q, k, v
 
 
-def _run_tree(q, k, v, seq_lens, tables, page, hratio, hk, scale, semantics="cpp", cfg=None, mnws=None):
+def _run_tree(q, k, v, seq_lens, tables, page, hratio, hk, scale, semantics="cpp", cfg=None, mnws=None, flags=0):
     tree = PrefixTreeCPP(page, semantics)
     if semantics == "cpp":
         tree.build_radix_tree(list(seq_lens), _padded(tables))
@@ -50,7 +50,7 @@ def _run_tree(q, k, v, seq_lens, tables, page, hratio, hk, scale, semantics="cpp
         out = torch.full_like(qd, float("nan"))
         lse = torch.full((q.shape[0], q.shape[2]), float("nan"), device=DEV)
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
-        prefix_attn_with_kvcache(qd, kd, vd, tree, scale, out, lse_out=lse, _status=status)
+        prefix_attn_with_kvcache(qd, kd, vd, tree, scale, out, lse_out=lse, _status=status, _flags=flags)
         torch.cuda.synchronize()
     finally:
         P.set_default_config(None)
@@ -156,6 +156,23 @@ def test_work_cuts_agree_with_oracle(opts, native_lib):
                             cfg=P.WorkConfig(**opts))
     ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
     _assert_close(out, lse, ref_o[:, 0], ref_l, torch.bfloat16)
+
+
+@pytest.mark.parametrize("cfg,factor", [(1, 2), (2, 2), (3, 2)])
+def test_dense_tiles_on_both_tensor_paths(cfg, factor, native_lib):
+    """Shared segments run on tcgen05/TMEM by default; the mma.sync version of the same tiles
+    (flag PAT_DENSE_MMA_SYNC = 8) must agree with it and with the oracle."""
+    w = scaled_down(cfg, factor)
+    q, k, v = make_values(w)
+    dtype = torch_dtype(w.dtype)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    out, lse, tree = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale)
+    assert tree.kernel_info.device_work(torch.device(DEV)).header.num_dense_items > 0
+    old, lse_old, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale,
+                                flags=8)
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
+    _assert_close(old, lse_old, ref_o[:, 0], ref_l, dtype)
 
 
 def test_sixteen_argument_form_with_python_scheduler(native_lib):
