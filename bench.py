@@ -337,7 +337,7 @@ def main():
     elif dominant == "dense_kernel":
         alg = kv_bytes(hdr.dense_unique_tokens)
     else:
-        alg = hdr.num_entries * hq * (D + 1) * 4 + B * hq * D * elt
+        alg = hdr.num_entries * w.group * (D + 1) * 4 + B * hq * D * elt
     achieved = alg / (k_ms[dominant] * 1e-3) / 1e9
     step_gbs = bytes_rank / (ms * 1e-3) / 1e9
     line = {
@@ -356,7 +356,7 @@ def main():
                           "achieved_gbs_per_gpu": step_gbs, "frac_of_measured_copy": step_gbs / peak,
                           "frac_of_8tbs": step_gbs / 8000.0},
         "kernels_ms": k_ms,
-        "work": {"stream_items": hdr.num_stream_items, "dense_items": hdr.num_dense_items,
+        "work": {"stream_items": hdr.num_stream_items, "dense_items": hdr.num_dense_items, "dense_ctas": hdr.num_dense_ctas,
                  "entries": hdr.num_entries, "segments": hdr.num_segments,
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
         "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},

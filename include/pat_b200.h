@@ -119,18 +119,21 @@ typedef struct pat_work_options {
     int32_t dense_min_rows;      /* segments with >= this many query rows use the dense kernel; 0 = default */
     int32_t chunk_tokens_min;    /* 0 = default */
     int32_t chunk_tokens_max;    /* 0 = default */
-    int32_t dense_chunk_tokens_max; /* 0 = default */
+    int32_t dense_piece_tokens_min; /* a dense CTA share is not cut below about this; 0 = default */
     int32_t items_per_sm;        /* 0 = default */
     int32_t disable_dense;       /* 1 = every segment goes through the streaming kernel */
     int32_t reserved;
 } pat_work_options;
 
 typedef struct pat_work_header {
-    int32_t batch, hratio, page_size;
-    int32_t num_stream_items, num_dense_items, num_entries, max_entries_per_query;
-    int32_t items_off, queries_off, pages_off, merge_indptr_off, merge_entries_off;
-    int32_t blob_words, num_segments;
-    int32_t max_page_id, reserved;
+    int32_t batch, hratio, page_size, kv_heads;
+    int32_t num_stream_items;       /* streaming items (<= 16 query rows, run for every KV head) */
+    int32_t num_dense_items;        /* dense items (<= 256 rows, one KV head each), grouped by CTA */
+    int32_t num_dense_ctas;         /* persistent CTAs of the dense kernel */
+    int32_t num_entries;            /* partial slots; one slot = hratio rows of (head_dim + 1) floats */
+    int32_t max_entries_per_list;
+    int32_t items_off, queries_off, pages_off, dense_cta_off, merge_indptr_off, merge_entries_off;
+    int32_t blob_words, num_segments, max_page_id;
     int64_t unique_tokens;          /* valid tokens summed over segments: every page counted once */
     int64_t stream_tokens;          /* tokens read by streaming items (a segment counts once per row chunk) */
     int64_t dense_tokens;           /* same for dense items */

@@ -31,18 +31,17 @@ class PlanBucket(C.Structure):
 
 class WorkOptions(C.Structure):
     _fields_ = [("num_sms", C.c_int32), ("dense_min_rows", C.c_int32), ("chunk_tokens_min", C.c_int32),
-                ("chunk_tokens_max", C.c_int32), ("dense_chunk_tokens_max", C.c_int32),
+                ("chunk_tokens_max", C.c_int32), ("dense_piece_tokens_min", C.c_int32),
                 ("items_per_sm", C.c_int32), ("disable_dense", C.c_int32), ("reserved", C.c_int32)]
 
 
 class WorkHeader(C.Structure):
-    _fields_ = [("batch", C.c_int32), ("hratio", C.c_int32), ("page_size", C.c_int32),
-                ("num_stream_items", C.c_int32), ("num_dense_items", C.c_int32),
-                ("num_entries", C.c_int32), ("max_entries_per_query", C.c_int32),
+    _fields_ = [("batch", C.c_int32), ("hratio", C.c_int32), ("page_size", C.c_int32), ("kv_heads", C.c_int32),
+                ("num_stream_items", C.c_int32), ("num_dense_items", C.c_int32), ("num_dense_ctas", C.c_int32),
+                ("num_entries", C.c_int32), ("max_entries_per_list", C.c_int32),
                 ("items_off", C.c_int32), ("queries_off", C.c_int32), ("pages_off", C.c_int32),
-                ("merge_indptr_off", C.c_int32), ("merge_entries_off", C.c_int32),
-                ("blob_words", C.c_int32), ("num_segments", C.c_int32),
-                ("max_page_id", C.c_int32), ("reserved", C.c_int32),
+                ("dense_cta_off", C.c_int32), ("merge_indptr_off", C.c_int32), ("merge_entries_off", C.c_int32),
+                ("blob_words", C.c_int32), ("num_segments", C.c_int32), ("max_page_id", C.c_int32),
                 ("unique_tokens", C.c_int64), ("stream_tokens", C.c_int64), ("dense_tokens", C.c_int64),
                 ("stream_unique_tokens", C.c_int64), ("dense_unique_tokens", C.c_int64)]
 

@@ -23,14 +23,14 @@ pat::WorkOptions to_options(const pat_work_options* o) {
     // Defaults: query-row tiles of 16 through the streaming kernel; segments with
     // more than 16 rows go through the dense (tensor-core tile) kernel in tiles of
     // up to 128 rows.
-    w.dense_rows = 128;
+    w.dense_rows = 256;
     w.dense_min_rows = 17;
     if (!o) return w;
     if (o->num_sms > 0) w.num_sms = o->num_sms;
     if (o->dense_min_rows > 0) w.dense_min_rows = o->dense_min_rows;
     if (o->chunk_tokens_min > 0) w.chunk_tokens_min = o->chunk_tokens_min;
     if (o->chunk_tokens_max > 0) w.chunk_tokens_max = o->chunk_tokens_max;
-    if (o->dense_chunk_tokens_max > 0) w.dense_chunk_tokens_max = o->dense_chunk_tokens_max;
+    if (o->dense_piece_tokens_min > 0) w.dense_piece_tokens_min = o->dense_piece_tokens_min;
     if (o->items_per_sm > 0) w.items_per_sm = o->items_per_sm;
     if (o->disable_dense) { w.dense_rows = 0; w.dense_min_rows = 1 << 30; }
     return w;
@@ -39,13 +39,14 @@ pat::WorkOptions to_options(const pat_work_options* o) {
 int map_work_error(int rc) { return rc == 0 ? PAT_OK : (rc == -1 ? PAT_ERR_BAD_ARGUMENT : PAT_ERR_BAD_PLAN); }
 
 void copy_header(const pat::WorkHeader& h, pat_work_header* out) {
-    out->batch = h.batch; out->hratio = h.hratio; out->page_size = h.page_size;
+    out->batch = h.batch; out->hratio = h.hratio; out->page_size = h.page_size; out->kv_heads = h.kv_heads;
     out->num_stream_items = h.num_stream_items; out->num_dense_items = h.num_dense_items;
-    out->num_entries = h.num_entries; out->max_entries_per_query = h.max_entries_per_query;
+    out->num_dense_ctas = h.num_dense_ctas;
+    out->num_entries = h.num_entries; out->max_entries_per_list = h.max_entries_per_list;
     out->items_off = h.items_off; out->queries_off = h.queries_off; out->pages_off = h.pages_off;
+    out->dense_cta_off = h.dense_cta_off;
     out->merge_indptr_off = h.merge_indptr_off; out->merge_entries_off = h.merge_entries_off;
-    out->blob_words = h.blob_words; out->num_segments = h.num_segments;
-    out->max_page_id = h.max_page_id; out->reserved = 0;
+    out->blob_words = h.blob_words; out->num_segments = h.num_segments; out->max_page_id = h.max_page_id;
     out->unique_tokens = h.unique_tokens; out->stream_tokens = h.stream_tokens;
     out->dense_tokens = h.dense_tokens;
     out->stream_unique_tokens = h.stream_unique_tokens;
@@ -56,7 +57,7 @@ void copy_header(const pat::WorkHeader& h, pat_work_header* out) {
 
 extern "C" {
 
-int pat_b200_abi_version(void) { return 1; }
+int pat_b200_abi_version(void) { return 2; }
 
 const char* pat_b200_strerror(int status) {
     switch (status) {

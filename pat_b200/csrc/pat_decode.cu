@@ -69,7 +69,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
                         a.v_head_stride, a.v_row_stride, a.v_page_stride);
     if (rc != PAT_OK) return rc;
 
-    const size_t rows = static_cast<size_t>(a.work.num_entries) * a.num_q_heads;
+    const size_t rows = static_cast<size_t>(a.work.num_entries) * a.work.hratio;   // hratio rows per entry
     float* part_o = static_cast<float*>(a.workspace);
     float* part_lse = part_o + rows * D;
 
@@ -106,8 +106,11 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         kern<<<static_cast<unsigned>(grid), kStreamWarps * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
-    if (a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE) && !(a.flags & PAT_DENSE_MMA_SYNC)) {
-        // dense tiles on tcgen05 / TMEM
+    const bool dense = a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE);
+    p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
+    p.num_items = a.work.num_dense_items;
+    if (dense && !(a.flags & PAT_DENSE_MMA_SYNC)) {
+        // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
         static bool configured[kMaxDevices] = {};
         auto kern = dense_tc_kernel<T, D>;
         constexpr int smem = TcSmem<D>::kRequest;
@@ -116,14 +119,14 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
                 return PAT_ERR_CUDA;
             configured[dev] = true;
         }
-        p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
-        p.num_items = a.work.num_dense_items;
-        const long long grid = static_cast<long long>(p.num_items) * a.num_kv_heads;
-        if (grid > 0x7fffffffLL) return PAT_ERR_TOO_LARGE;
-        kern<<<static_cast<unsigned>(grid), kTcThreads, smem, stream>>>(p, kmap, vmap);
+        DenseTcParams dp{};
+        dp.a = p;
+        dp.cta_begin = a.work_blob + a.work.dense_cta_off;
+        kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, stream>>>(dp, kmap, vmap);
         ++launches;
-    } else if (a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE)) {
-        // the same tiles on the legacy mma.sync path (kept for comparison)
+    } else if (dense) {
+        // the same items on the legacy mma.sync path (kept for comparison): one CTA per
+        // (item, 128-row half)
         static bool configured[kMaxDevices] = {};
         auto kern = dense_kernel<T, D>;
         constexpr int smem = dense_smem_bytes<D>();
@@ -132,11 +135,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
                 return PAT_ERR_CUDA;
             configured[dev] = true;
         }
-        p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
-        p.num_items = a.work.num_dense_items;
-        const long long grid = static_cast<long long>(p.num_items) * a.num_kv_heads;
-        if (grid > 0x7fffffffLL) return PAT_ERR_TOO_LARGE;
-        kern<<<static_cast<unsigned>(grid), (kDenseWarps + 1) * 32, smem, stream>>>(p, kmap, vmap);
+        kern<<<dim3(static_cast<unsigned>(a.work.num_dense_items), 2), (kDenseWarps + 1) * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
     if (!(a.flags & PAT_SKIP_MERGE)) {
@@ -151,6 +150,8 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         mp.out_head_stride = a.out_head_stride;
         mp.batch = a.batch;
         mp.num_q_heads = a.num_q_heads;
+        mp.kv_heads = a.num_kv_heads;
+        mp.hratio = a.work.hratio;
         const int total = a.batch * a.num_q_heads;
         const int warps_per_cta = 8;
         merge_kernel<T, D><<<(total + warps_per_cta - 1) / warps_per_cta, warps_per_cta * 32, 0, stream>>>(mp);
@@ -167,8 +168,9 @@ extern "C" {
 
 size_t pat_b200_workspace_bytes(const pat_work_header* work, int num_q_heads, int head_dim) {
     if (!work || num_q_heads <= 0 || head_dim <= 0) return 0;
-    const size_t rows = static_cast<size_t>(work->num_entries) * num_q_heads;
-    // partial outputs + partial LSEs, rounded up to 256 B
+    (void)num_q_heads;
+    // one entry = hratio rows (the query heads of one KV head): partial outputs + partial LSEs
+    const size_t rows = static_cast<size_t>(work->num_entries) * static_cast<size_t>(work->hratio);
     const size_t bytes = rows * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
     return (bytes + 255) / 256 * 256 + 256;
 }
@@ -182,7 +184,7 @@ int pat_b200_decode(const pat_decode_args* args, void* stream_handle) {
     if (a.batch <= 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0 || a.num_pages <= 0) return PAT_ERR_BAD_ARGUMENT;
     if (a.num_q_heads % a.num_kv_heads != 0) return PAT_ERR_BAD_ARGUMENT;
     if (a.work.batch != a.batch || a.work.hratio != a.num_q_heads / a.num_kv_heads ||
-        a.work.page_size != a.page_size)
+        a.work.page_size != a.page_size || a.work.kv_heads != a.num_kv_heads)
         return PAT_ERR_BAD_PLAN;
     if (a.work.max_page_id >= a.num_pages) return PAT_ERR_BAD_PLAN;
     if (a.head_dim != 64 && a.head_dim != 128) return PAT_ERR_UNSUPPORTED;

@@ -1,25 +1,26 @@
 // Dense-tile attention on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// One CTA = one dense work item (up to 128 query rows that share a KV chunk) x one KV head.
-// Replaces the reference's M=64 mma.sync tile (csrc/pat_fwd_kernel.h:25-299,
+// Persistent kernel, one CTA per SM.  A CTA walks its share of dense work items (each item:
+// up to 256 query rows - two 128-row tiles - of one KV head over a range of tokens of a
+// shared segment); the shares are cut on the host so that every CTA streams the same number
+// of tokens.  Replaces the reference's M=64 mma.sync tile (csrc/pat_fwd_kernel.h:25-299,
 // csrc/kernel_traits.h:45-123) for segments that many queries share.
 //
-//   warps 0-3 (128 threads): thread r owns query row r = TMEM lane r.  Per 64-token tile it
-//            reads its row of S = Q K^T from TMEM (tcgen05.ld), does the online softmax with
-//            no cross-thread traffic, and writes P (bf16/fp16) to shared memory.
-//   thread 0 additionally issues the MMAs: S_j = Q K_j^T (M128 N64 K16 x D/16) one tile
-//            ahead, O += P_j V_j (M128 N=D K16 x 4) after the tile's softmax; completion is
-//            tracked with tcgen05.commit on mbarriers.
-//   warp 4 / warp 5: TMA producers for K and for V, 2 stages of 64 tokens each (boxes of
-//            16 tokens x 64 elements, 128-byte swizzle - the layout the UMMA shared-memory
-//            descriptors below describe).  A K stage is released as soon as its S = Q K^T has
-//            completed and a V stage when its P V has, so both run about two tiles ahead.
+//   warps 0-3 / 4-7: softmax groups 0 / 1.  Thread r of group w owns query row 128 w + r
+//            (= TMEM lane r).  Per 64-token tile it reads its row of S = Q K^T from TMEM
+//            (tcgen05.ld), does the online softmax without any cross-thread traffic and writes
+//            P (bf16/fp16) to shared memory; at the end of an item it reads O from TMEM and
+//            stores the normalised fp32 partial and its LSE.
+//   warp 8:  TMA producer: 4 stages of 64 tokens (K and V boxes of 16 tokens x 64 elements,
+//            128-byte swizzle - the layout the UMMA shared-memory descriptors describe).
+//   warp 9:  one thread issues every MMA: S_w(j+1) = Q_w K^T (M128 N64 K16 x D/16) one tile
+//            ahead of the softmax, then O_w += P_w(j) V (M128 N=D K16 x 4); completion is
+//            signalled with tcgen05.commit on mbarriers.
 //
-// TMEM: 256 columns per CTA: S double-buffered (2 x 64 fp32 columns) + O (D columns).
-// Shared memory: 112.25 KB per CTA, so two CTAs share an SM (and its 512 TMEM columns); one
-// CTA's softmax overlaps the other's MMAs.
-// The running maximum is only raised when a tile exceeds it by more than 2^8 (the exponent
-// offset cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
+// Both row tiles share the staged K/V tile, so a shared page is read from HBM (and from L2)
+// once per 256 query rows.  TMEM (512 columns): S double-buffered per group (4 x 64) + O per
+// group (2 x D).  The running maximum is only raised when a tile exceeds it by more than 2^8
+// (the offset cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
 // Every mbarrier wait is bounded; a wait that gives up records a code in the status word,
 // later waits are skipped and the CTA still frees its TMEM before it returns.
 #pragma once
@@ -29,27 +30,22 @@
 namespace pat {
 
 constexpr int kTcTile = 64;                 // tokens per tile
-constexpr int kTcStages = 2;
-constexpr int kTcThreads = 192;
-constexpr int kTcTmemCols = 256;
+constexpr int kTcStages = 4;
+constexpr int kTcThreads = 320;
+constexpr int kTcTmemCols = 512;
 constexpr float kTcLazyLog2 = 8.0f;
 
 template <int D> struct TcSmem {
     static constexpr int kBoxes = D / 64;
-    static constexpr int kQBytes = kBoxes * 128 * 128;          // [box][128 rows][128 B]
+    static constexpr int kQBytes = kBoxes * 128 * 128;          // per row tile: [box][128 rows][128 B]
     static constexpr int kKBytes = kBoxes * kTcTile * 128;      // [box][64 tokens][128 B]
-    static constexpr int kVBytes = kKBytes;
-    static constexpr int kPBytes = 128 * 128;                   // [128 rows][64 tokens x 2 B]
+    static constexpr int kStageBytes = 2 * kKBytes;             // K then V
+    static constexpr int kPBytes = 128 * 128;                   // per row tile: [128 rows][64 tokens x 2 B]
     static constexpr int kQOff = 0;
-    static constexpr int kKOff = kQOff + kQBytes;
-    static constexpr int kVOff = kKOff + kTcStages * kKBytes;
-    static constexpr int kPOff = kVOff + kTcStages * kVBytes;
-    static constexpr int kBarOff = kPOff + kPBytes;             // 11 mbarriers + tmem base word
-    static constexpr int kUsed = kBarOff + 128;
-    // Fixed request (also for D = 64) so that exactly two CTAs fit on an SM: a third one would
-    // only wait for TMEM columns.
-    static constexpr int kRequest = 114944;
-    static_assert(kUsed <= kRequest, "shared memory layout exceeds the per-CTA budget");
+    static constexpr int kPOff = kQOff + 2 * kQBytes;
+    static constexpr int kStageOff = kPOff + 2 * kPBytes;
+    static constexpr int kBarOff = kStageOff + kTcStages * kStageBytes;
+    static constexpr int kRequest = kBarOff + 256;              // 17 mbarriers + tmem base word + flag
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------
@@ -76,12 +72,6 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
-
-#define PAT_TMEM_LIST64(p) \
-    p(0) p(1) p(2) p(3) p(4) p(5) p(6) p(7) p(8) p(9) p(10) p(11) p(12) p(13) p(14) p(15) \
-    p(16) p(17) p(18) p(19) p(20) p(21) p(22) p(23) p(24) p(25) p(26) p(27) p(28) p(29) p(30) p(31) \
-    p(32) p(33) p(34) p(35) p(36) p(37) p(38) p(39) p(40) p(41) p(42) p(43) p(44) p(45) p(46) p(47) \
-    p(48) p(49) p(50) p(51) p(52) p(53) p(54) p(55) p(56) p(57) p(58) p(59) p(60) p(61) p(62) p(63)
 
 // 64 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
@@ -154,11 +144,17 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+struct DenseTcParams {
+    AttnParams a;
+    const int32_t* cta_begin;   // [num_ctas + 1] first dense item of each CTA
+};
+
 // ------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(kTcThreads)
-dense_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+__global__ void __launch_bounds__(kTcThreads, 1)
+dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     using L = TcSmem<D>;
+    const AttnParams& p = dp.a;
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     const uint32_t base = smem_u32(tc_smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -166,228 +162,285 @@ dense_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, co
         if (tid == 0 && p.status) atomicExch(p.status, 10);
         return;
     }
-    const uint32_t sQ = base + L::kQOff, sK = base + L::kKOff, sV = base + L::kVOff, sP = base + L::kPOff;
+    const uint32_t sQ = base + L::kQOff, sP = base + L::kPOff, sStage = base + L::kStageOff;
     const uint32_t bars = base + L::kBarOff;
-    const uint32_t bar_full_k = bars, bar_full_v = bars + 16, bar_empty_k = bars + 32, bar_empty_v = bars + 48,
-                   bar_s = bars + 64, bar_o = bars + 80;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 96);
-
-    const int item_idx = blockIdx.x / p.kv_heads;
-    const int kvh = blockIdx.x - item_idx * p.kv_heads;
-    const int32_t* it = p.items + static_cast<size_t>(item_idx) * 8;
-    const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
-              entry_base = __ldg(it + 4);
-    const int rows_valid = nq * p.hratio;
-    const int n_sub = (kv_len + 15) >> 4;
-    const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
+    // barrier map (8 bytes each): full[4] empty[4] s_full[w][b] (4) p_ready[2] o_done[2] q_ready
+    const uint32_t bar_full = bars, bar_empty = bars + 32, bar_s = bars + 64, bar_p = bars + 96, bar_o = bars + 112,
+                   bar_q = bars + 128;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 144);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 152);
 
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
-    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 104);
     if (tid == 0) *poisoned = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
     __syncthreads();
     if (*poisoned) return;
 
+    const int item_lo = __ldg(dp.cta_begin + blockIdx.x), item_hi = __ldg(dp.cta_begin + blockIdx.x + 1);
+
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
-        for (int i = 0; i < 11; ++i) mbar_init(bars + 8 * i, 1);   // full_k/v[2] empty_k/v[2] s[2] o
+        for (int i = 0; i < 8; ++i) mbar_init(bar_full + 8 * i, 1);    // full[4], empty[4]
+        for (int i = 0; i < 4; ++i) mbar_init(bar_s + 8 * i, 1);       // s_full
+        for (int i = 0; i < 2; ++i) mbar_init(bar_p + 8 * i, 128);     // p_ready: every thread of a group
+        for (int i = 0; i < 2; ++i) mbar_init(bar_o + 8 * i, 1);       // o_done
+        mbar_init(bar_q, 256);                                         // q_ready: both groups
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTcTmemCols);
-
-    // ---- Q rows into the swizzled K-major layout (thread r = row r) ------------------
-    if (tid < 128) {
-        const int r = tid;
-        const uint4* src = nullptr;
-        if (r < rows_valid) {
-            const int qi = r / p.hratio, g = r - qi * p.hratio;
-            const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
-                         static_cast<int64_t>(kvh * p.hratio + g) * p.q_head_stride;
-            src = reinterpret_cast<const uint4*>(q);
-        }
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-            const uint4 v = src ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-            const uint32_t dst = sQ + (c >> 3) * (128 * 128) + swz128(r, c & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-        }
-        fence_async_smem();
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-
     const int tiles_per_page = p.page_size >> 4;
-    const int32_t* item_pages = p.pages + page_off;
 
-    if (warp >= 4) {
-        // ---- TMA producers: warp 4 streams K, warp 5 streams V -----------------------------
-        const bool is_k = warp == 4;
-        const CUtensorMap* map = is_k ? &kmap : &vmap;
-        const uint32_t stage0 = is_k ? sK : sV;
-        const uint32_t full = is_k ? bar_full_k : bar_full_v;
-        const uint32_t empty = is_k ? bar_empty_k : bar_empty_v;
+    if (warp == 8) {
+        // ---- TMA producer ----------------------------------------------------------------
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
-            if (j >= kTcStages && ok) ok = mbar_wait(empty + 8 * s, ((j >> 1) - 1) & 1);
-            if (!ok) break;
-            const int subs = min(4, n_sub - j * 4);
-            if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
-            __syncwarp();
-            if (lane < subs) {
-                const int t = j * 4 + lane;
-                const int page = __ldg(item_pages + t / tiles_per_page);
-                const int row0 = (t % tiles_per_page) << 4;
+        int g = 0;
+        for (int item = item_lo; item < item_hi && ok; ++item) {
+            const int32_t* it = p.items + static_cast<size_t>(item) * 8;
+            const int page_off = __ldg(it + 2), kv_len = __ldg(it + 3), kvh = __ldg(it + 5);
+            const int n_sub = (kv_len + 15) >> 4;
+            const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
+            const int32_t* item_pages = p.pages + page_off;
+            for (int j = 0; j < n_tiles; ++j, ++g) {
+                const int s = g % kTcStages;
+                if (g >= kTcStages) ok = mbar_wait(bar_empty + 8 * s, ((g / kTcStages) - 1) & 1);
+                if (!ok) break;
+                const int subs = min(4, n_sub - j * 4);
+                if (lane == 0) mbar_expect_tx(bar_full + 8 * s, subs * (2 * L::kBoxes * 2048));
+                __syncwarp();
+                if (lane < subs) {
+                    const int t = j * 4 + lane;
+                    const int page = __ldg(item_pages + t / tiles_per_page);
+                    const int row0 = (t % tiles_per_page) << 4;
+                    const uint32_t dst = sStage + s * L::kStageBytes + lane * 2048;
 #pragma unroll
-                for (int b = 0; b < L::kBoxes; ++b)
-                    tma_load_4d(stage0 + s * L::kKBytes + b * (kTcTile * 128) + lane * 2048, map, full + 8 * s,
-                                b * 64, kvh, row0, page);
+                    for (int b = 0; b < L::kBoxes; ++b) {
+                        tma_load_4d(dst + b * (kTcTile * 128), &kmap, bar_full + 8 * s, b * 64, kvh, row0, page);
+                        tma_load_4d(dst + L::kKBytes + b * (kTcTile * 128), &vmap, bar_full + 8 * s, b * 64, kvh, row0, page);
+                    }
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
         if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
         return;
     }
 
-    // ---- softmax threads (thread 0 also issues the MMAs) ------------------------------------
-    const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
-    const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const uint32_t tmem_o = tmem_base + 2 * kTcTile;
+    if (warp == 9) {
+        // ---- MMA issuer (one thread) ---------------------------------------------------------
+        if (lane != 0) return;
+        const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
+        const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
+        bool ok = true;
+        int g = 0, g1 = 0, n_item = 0;
+        for (int item = item_lo; item < item_hi; ++item, ++n_item) {
+            const int32_t* it = p.items + static_cast<size_t>(item) * 8;
+            const int nq = __ldg(it + 1), kv_len = __ldg(it + 3);
+            const bool two = nq * p.hratio > 128;
+            const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
+            if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
+            tc_fence_after();
+
+            auto issue_qk = [&](int j) {
+                const int s = (g + j) % kTcStages;
+                if (ok) ok = mbar_wait(bar_full + 8 * s, ((g + j) / kTcStages) & 1);
+                tc_fence_after();
+                const uint32_t k_addr = sStage + s * L::kStageBytes;
+                for (int w = 0; w < (two ? 2 : 1); ++w) {
+                    const int t = (w == 0 ? g : g1) + j;               // this group's running tile index
+                    const uint32_t d_tmem = tmem_base + w * 128 + (t & 1) * kTcTile;
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint64_t a = umma_desc_kmajor(sQ + w * L::kQBytes + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
+                        const uint64_t b = umma_desc_kmajor(k_addr + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
+                        tc_mma(d_tmem, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar_s + 8 * (2 * w + (t & 1)));
+                }
+            };
+
+            issue_qk(0);
+            for (int j = 0; j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) issue_qk(j + 1);
+                const int s = (g + j) % kTcStages;
+                const uint32_t v_addr = sStage + s * L::kStageBytes + L::kKBytes;
+                for (int w = 0; w < (two ? 2 : 1); ++w) {
+                    const int t = (w == 0 ? g : g1) + j;
+                    if (ok) ok = mbar_wait(bar_p + 8 * w, t & 1);      // P_w(j) written, S_w(j) consumed
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < kTcTile / 16; ++ks) {
+                        const uint64_t a = umma_desc_kmajor(sP + w * L::kPBytes + ks * 32);
+                        const uint64_t b = umma_desc_mnmajor(v_addr + ks * 2048, kTcTile * 128);
+                        tc_mma(tmem_base + 256 + w * 128, a, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_o + 8 * w);
+                }
+                tc_commit(bar_empty + 8 * s);                           // K/V stage free when both are done
+            }
+            g += n_tiles;
+            if (two) g1 += n_tiles;
+        }
+        if (!ok && p.status) atomicExch(p.status, 13);
+        return;
+    }
+
+    // ---- softmax groups -----------------------------------------------------------------------
+    const int w = warp >> 2;                    // group 0 / 1
+    const int r = tid & 127;                    // row within the 128-row tile = TMEM lane
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t tmem_s = lane_addr + w * 128, tmem_o = lane_addr + 256 + w * 128;
     const float c = p.scale_log2;
     bool ok = true;
+    int t = 0;                                  // this group's running tile index
+    int g = 0;                                  // running tile index of the stage ring
+    int n_item = 0;
+    for (int item = item_lo; item < item_hi; ++item) {
+        const int32_t* it = p.items + static_cast<size_t>(item) * 8;
+        const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kv_len = __ldg(it + 3), entry_base = __ldg(it + 4),
+                  kvh = __ldg(it + 5);
+        const int rows_valid = nq * p.hratio;
+        const bool active = (w == 0) || rows_valid > 128;
+        const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
+        const int row = w * 128 + r;
 
-    auto issue_qk = [&](int j) {       // thread 0: S[j & 1] = Q K_j^T
-        const int s = j & 1;
-        if (ok) ok = mbar_wait(bar_full_k + 8 * s, (j >> 1) & 1);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            const uint64_t a = umma_desc_kmajor(sQ + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
-            const uint64_t b = umma_desc_kmajor(sK + s * L::kKBytes + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
-            tc_mma(tmem_base + s * kTcTile, a, b, idesc_qk, ks > 0 ? 1u : 0u);
-        }
-        tc_commit(bar_s + 8 * s);
-        tc_commit(bar_empty_k + 8 * s);      // the K stage is free once this product has completed
-    };
-
-    if (tid == 0) issue_qk(0);
-    float m_used = -INFINITY, l = 0.f;
-    for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (tid == 0 && j + 1 < n_tiles) issue_qk(j + 1);
-        if (ok) ok = mbar_wait(bar_s + 8 * s, (j >> 1) & 1);
-        tc_fence_after();
-        float sc[64];
-        tmem_ld64(lane_addr + s * kTcTile, sc);
-        const int valid = min(kTcTile, kv_len - j * kTcTile);
-        if (valid < kTcTile) {
-#pragma unroll
-            for (int i = 0; i < 64; ++i)
-                if (i >= valid) sc[i] = -INFINITY;
-        }
-        float mx = sc[0];
-#pragma unroll
-        for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sc[i]);
-
-        // the previous PV must be done before P is overwritten or O is rescaled
-        if (j > 0 && ok) ok = mbar_wait(bar_o, (j - 1) & 1);
-        tc_fence_after();
-        const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
-        if (j > 0 && __any_sync(kFullMask, raise)) {
-            const float alpha = raise ? fast_exp2((m_used - mx) * c) : 1.f;
-            l *= alpha;
-#pragma unroll 1
-            for (int h = 0; h < D / 64; ++h) {
-                float ov[64];
-                tmem_ld64(lane_addr + 2 * kTcTile + h * 64, ov);
-#pragma unroll
-                for (int i = 0; i < 64; ++i) ov[i] *= alpha;
-                tmem_st64(lane_addr + 2 * kTcTile + h * 64, ov);
+        // Q rows of this item into the swizzled K-major layout (every MMA of the previous item has
+        // completed: its last o_done was awaited in the epilogue below)
+        if (active) {
+            const uint4* src = nullptr;
+            if (row < rows_valid) {
+                const int qi = row / p.hratio, gg = row - qi * p.hratio;
+                const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
+                             static_cast<int64_t>(kvh * p.hratio + gg) * p.q_head_stride;
+                src = reinterpret_cast<const uint4*>(q);
             }
-        }
-        if (raise) m_used = mx;
-        const float off = m_used * c;
-        float sum = 0.f;
-        uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
-            const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
-            sum += p0 + p1;
-            packed[i] = Elt<T>::pack(p0, p1);
+            for (int ch = 0; ch < D / 8; ++ch) {
+                const uint4 v = src ? __ldg(src + ch) : make_uint4(0, 0, 0, 0);
+                const uint32_t dst = sQ + w * L::kQBytes + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            }
+            fence_async_smem();
         }
-        l += sum;
-        {   // row tid of P: 8 chunks of 16 B, swizzled like a [128 x 128 B] K-major tile
-            const int r = tid;
+        tc_fence_before();
+        mbar_arrive(bar_q);
+        if (!active) {
+            // an idle group must not run ahead: its next arrival may only count for the next phase
+            if (ok) ok = mbar_wait(bar_q, n_item & 1);
+            g += n_tiles;
+            ++n_item;
+            continue;
+        }
+        ++n_item;
+
+        float m_used = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_tiles; ++j, ++t) {
+            if (ok) ok = mbar_wait(bar_s + 8 * (2 * w + (t & 1)), (t >> 1) & 1);
+            tc_fence_after();
+            float sc[64];
+            tmem_ld64(tmem_s + (t & 1) * kTcTile, sc);
+            const int valid = min(kTcTile, kv_len - j * kTcTile);
+            if (valid < kTcTile) {
 #pragma unroll
-            for (int k8 = 0; k8 < 8; ++k8) {
-                const uint32_t dst = sP + swz128(r, k8);
+                for (int i = 0; i < 64; ++i)
+                    if (i >= valid) sc[i] = -INFINITY;
+            }
+            float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
+#pragma unroll
+            for (int i = 4; i < 64; i += 4) {
+                mx0 = fmaxf(mx0, fmaxf(sc[i], sc[i + 1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[i + 2], sc[i + 3]));
+            }
+            const float mx = fmaxf(mx0, mx1);
+
+            // the previous PV of this group must be done before P is overwritten or O is rescaled
+            if (j > 0 && ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
+            tc_fence_after();
+            const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
+            if (j > 0 && __any_sync(kFullMask, raise)) {
+                const float alpha = raise ? fast_exp2((m_used - mx) * c) : 1.f;
+                l *= alpha;
+#pragma unroll 1
+                for (int h = 0; h < D / 64; ++h) {
+                    float ov[64];
+                    tmem_ld64(tmem_o + h * 64, ov);
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) ov[i] *= alpha;
+                    tmem_st64(tmem_o + h * 64, ov);
+                }
+            }
+            if (raise) m_used = mx;
+            const float off = m_used * c;
+            float sum0 = 0.f, sum1 = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
+                const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
+                sum0 += p0;
+                sum1 += p1;
+                packed[i] = Elt<T>::pack(p0, p1);
+            }
+            l += sum0 + sum1;
+#pragma unroll
+            for (int k8 = 0; k8 < 8; ++k8) {   // row r of P: 8 chunks of 16 B, swizzled like a [128 x 128 B] tile
+                const uint32_t dst = sP + w * L::kPBytes + swz128(r, k8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * k8]), "r"(packed[4 * k8 + 1]),
                              "r"(packed[4 * k8 + 2]), "r"(packed[4 * k8 + 3]) : "memory");
             }
-        }
-        if (valid < kTcTile) {
-            // V rows past the valid tokens may hold anything (stale tiles, never written pages):
-            // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
-            if (ok) ok = mbar_wait(bar_full_v + 8 * s, (j >> 1) & 1);
-            const int rows = kTcTile - valid;
-            const int chunks = rows * 8 * L::kBoxes;
-            for (int i = tid; i < chunks; i += 128) {
-                const int b = i / (rows * 8);
-                const int rem = i - b * rows * 8;
-                const int row = valid + (rem >> 3);
-                const uint32_t dst = sV + s * L::kVBytes + b * (kTcTile * 128) + row * 128 + ((rem & 7) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+            if (valid < kTcTile && w == 0) {
+                // V rows past the valid tokens may hold anything (stale tiles, never written pages):
+                // zero them so that P = 0 times garbage cannot make a NaN.  The stage has landed
+                // (its S was computed from it) and both groups' P V products are issued after
+                // group 0 has arrived below.
+                const int s = (g + j) % kTcStages;
+                const int rows = kTcTile - valid;
+                const int chunks = rows * 8 * L::kBoxes;
+                for (int i = r; i < chunks; i += 128) {
+                    const int b = i / (rows * 8);
+                    const int rem = i - b * rows * 8;
+                    const int vrow = valid + (rem >> 3);
+                    const uint32_t dst = sStage + s * L::kStageBytes + L::kKBytes + b * (kTcTile * 128) + vrow * 128 + ((rem & 7) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+                }
             }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_p + 8 * w);
         }
-        fence_async_smem();
-        tc_fence_before();
-        named_bar_sync(1, 128);
-        if (tid == 0) {
-            if (ok) ok = mbar_wait(bar_full_v + 8 * s, (j >> 1) & 1);
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < kTcTile / 16; ++ks) {
-                const uint64_t a = umma_desc_kmajor(sP + ks * 32);
-                const uint64_t b = umma_desc_mnmajor(sV + s * L::kVBytes + ks * 2048, kTcTile * 128);
-                tc_mma(tmem_o, a, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-            }
-            tc_commit(bar_o);
-            tc_commit(bar_empty_v + 8 * s);
-        }
-    }
+        g += n_tiles;
 
-    // ---- epilogue: O / l -> fp32 partial, LSE -------------------------------------------------
-    if (ok) ok = mbar_wait(bar_o, (n_tiles - 1) & 1);
-    tc_fence_after();
-    if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
-    {
-        const int r = tid;
-        const bool store = ok && r < rows_valid;
-        size_t slot = 0;
-        if (r < rows_valid) {
-            const int qi = r / p.hratio, g = r - qi * p.hratio;
-            slot = static_cast<size_t>(entry_base + qi) * p.num_q_heads + kvh * p.hratio + g;
-        }
-        const float inv = 1.f / l;
-#pragma unroll 1
-        for (int h = 0; h < D / 64; ++h) {
-            float ov[64];
-            tmem_ld64(lane_addr + 2 * kTcTile + h * 64, ov);
-            if (store) {
-                float4* dst = reinterpret_cast<float4*>(p.part_o + slot * D + h * 64);
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+        // ---- item epilogue: O / l -> fp32 partial, LSE ---------------------------------------------
+        if (ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
+        tc_fence_after();
+        {
+            const bool store = ok && row < rows_valid;
+            size_t slot = 0;
+            if (row < rows_valid) {
+                const int qi = row / p.hratio, gg = row - qi * p.hratio;
+                slot = static_cast<size_t>(entry_base + qi) * p.hratio + gg;
             }
+            const float inv = 1.f / l;
+#pragma unroll 1
+            for (int h = 0; h < D / 64; ++h) {
+                float ov[64];
+                tmem_ld64(tmem_o + h * 64, ov);
+                if (store) {
+                    float4* dst = reinterpret_cast<float4*>(p.part_o + slot * D + h * 64);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+                }
+            }
+            if (store) p.part_lse[slot] = m_used * p.scale + logf(l);
         }
-        if (store) p.part_lse[slot] = m_used * p.scale + logf(l);
     }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     tc_fence_before();
-    named_bar_sync(1, 128);
+    named_bar_sync(1, 256);
     if (warp == 0) tmem_dealloc(tmem_base, kTcTmemCols);
 }
 

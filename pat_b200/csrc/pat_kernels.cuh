@@ -234,7 +234,8 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
         }
         const float inv = 1.f / L;
         const int qi = row / p.hratio, gg = row - qi * p.hratio;
-        const size_t slot = static_cast<size_t>(entry_base + qi) * p.num_q_heads + kvh * p.hratio + gg;
+        // entry of (query qi, KV head kvh) = entry_base + qi * kv_heads + kvh; hratio rows per entry
+        const size_t slot = (static_cast<size_t>(entry_base) + static_cast<size_t>(qi) * p.kv_heads + kvh) * p.hratio + gg;
         *reinterpret_cast<float4*>(p.part_o + slot * D + v4 * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         if (v4 == 0) p.part_lse[slot] = g * p.scale + logf(L);
     }
@@ -253,13 +254,15 @@ dense_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S];
 
+    // One dense item (<= 256 rows, its own KV head) per blockIdx.x; blockIdx.y picks the
+    // 128-row half this CTA computes.
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int item_idx = blockIdx.x / p.kv_heads;
-    const int kvh = blockIdx.x - item_idx * p.kv_heads;
-    const int32_t* it = p.items + static_cast<size_t>(item_idx) * 8;
+    const int32_t* it = p.items + static_cast<size_t>(blockIdx.x) * 8;
     const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
-              entry_base = __ldg(it + 4);
+              entry_base = __ldg(it + 4), kvh = __ldg(it + 5);
     const int rows_valid = nq * p.hratio;
+    const int half_base = blockIdx.y * (W * 16);
+    if (half_base >= rows_valid) return;
 
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
@@ -310,7 +313,7 @@ dense_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const
     }
 
     // ---- consumer warps -----------------------------------------------------------
-    const int row_base = warp * 16;
+    const int row_base = half_base + warp * 16;
     const bool active = row_base < rows_valid;   // warps without rows still release stages
     uint32_t qf[D / 16][4];
     load_q_frags<T, D>(qf, p, p.queries + q_off, row_base, rows_valid, kvh, lane);
@@ -363,7 +366,7 @@ dense_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const
         const int row = row_base + (lane >> 2) + 8 * h;
         if (row >= rows_valid) continue;
         const int qi = row / p.hratio, gg = row - qi * p.hratio;
-        const size_t slot = static_cast<size_t>(entry_base + qi) * p.num_q_heads + kvh * p.hratio + gg;
+        const size_t slot = static_cast<size_t>(entry_base + qi) * p.hratio + gg;   // dense entries are per KV head
         const float inv = 1.f / l[h];
         float* dst = p.part_o + slot * D + col;
 #pragma unroll
@@ -384,7 +387,7 @@ struct MergeParams {
     void* out;
     float* lse_out;           // optional [batch, H]
     int64_t out_batch_stride, out_head_stride;
-    int batch, num_q_heads;
+    int batch, num_q_heads, kv_heads, hratio;
 };
 
 template <typename T, int D>
@@ -394,12 +397,14 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= p.batch * p.num_q_heads) return;
     const int b = row / p.num_q_heads, h = row - b * p.num_q_heads;
-    const int lo = __ldg(p.indptr + b), n = __ldg(p.indptr + b + 1) - lo;
+    const int kvh = h / p.hratio, g = h - kvh * p.hratio;
+    const int list = b * p.kv_heads + kvh;             // one list of entries per (request, KV head)
+    const int lo = __ldg(p.indptr + list), n = __ldg(p.indptr + list + 1) - lo;
     const int32_t* ent = p.entries + lo;
 
     float gmax = -INFINITY;
     for (int i = lane; i < n; i += 32)
-        gmax = fmaxf(gmax, __ldg(p.part_lse + static_cast<size_t>(__ldg(ent + i)) * p.num_q_heads + h));
+        gmax = fmaxf(gmax, __ldg(p.part_lse + static_cast<size_t>(__ldg(ent + i)) * p.hratio + g));
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(kFullMask, gmax, d));
 
@@ -408,7 +413,7 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
     for (int k = 0; k < kPer; ++k) acc[k] = 0.f;
     float wsum = 0.f;
     for (int i = 0; i < n; ++i) {
-        const size_t slot = static_cast<size_t>(__ldg(ent + i)) * p.num_q_heads + h;
+        const size_t slot = static_cast<size_t>(__ldg(ent + i)) * p.hratio + g;
         const float lse = __ldg(p.part_lse + slot);
         const float w = (lse == -INFINITY) ? 0.f : __expf(lse - gmax);
         wsum += w;

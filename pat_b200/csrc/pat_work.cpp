@@ -172,36 +172,29 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         }
     }
 
-    // ---- 4. chunk sizes -------------------------------------------------------
+    // ---- 4. classes and chunk sizes ---------------------------------------------
     const int q_per_stream = std::max(1, opt.stream_rows / hratio);
     const int q_per_dense = opt.dense_rows > 0 ? std::max(1, opt.dense_rows / hratio) : 0;
     auto is_dense = [&](const Segment& sg) {
         return q_per_dense > 0 && static_cast<int64_t>(sg.queries.size()) * hratio >= opt.dense_min_rows;
     };
-    int64_t stream_cost = 0, dense_cost = 0, unique_tokens = 0;
+    int64_t stream_cost = 0, unique_tokens = 0;
     for (const Segment& sg : segs) {
         unique_tokens += sg.tokens;
         const int nq = static_cast<int>(sg.queries.size());
         if (is_dense(sg)) {
-            dense_cost += sg.tokens * ceil_div(nq, q_per_dense);
             header_.dense_unique_tokens += sg.tokens;
         } else {
             stream_cost += sg.tokens * ceil_div(nq, q_per_stream);
             header_.stream_unique_tokens += sg.tokens;
         }
     }
-    auto pick_chunk = [&](int64_t cost, int cmin, int cmax, int per_sm) {
-        int64_t want = cost * kv_heads / std::max<int64_t>(1, static_cast<int64_t>(opt.num_sms) * per_sm);
-        want = (want + page_size - 1) / page_size * page_size;
-        want = std::max<int64_t>(want, std::max(cmin, page_size));
-        want = std::min<int64_t>(want, std::max(cmax, page_size));
-        return static_cast<int>(want);
-    };
-    const int stream_chunk = pick_chunk(stream_cost, opt.chunk_tokens_min, opt.chunk_tokens_max, opt.items_per_sm);
-    const int dense_chunk = pick_chunk(dense_cost, opt.chunk_tokens_min, opt.dense_chunk_tokens_max,
-                                       std::max(1, opt.items_per_sm / 4));
+    int64_t want = stream_cost * kv_heads / std::max<int64_t>(1, static_cast<int64_t>(opt.num_sms) * opt.items_per_sm);
+    want = (want + page_size - 1) / page_size * page_size;
+    want = std::max<int64_t>(want, std::max(opt.chunk_tokens_min, page_size));
+    want = std::min<int64_t>(want, std::max(opt.chunk_tokens_max, page_size));
+    const int stream_chunk = static_cast<int>(want);
 
-    // ---- 5. items -------------------------------------------------------------
     std::vector<int32_t> queries_sec, pages_sec;
     for (Segment& sg : segs) {
         sg.q_off = static_cast<int32_t>(queries_sec.size());
@@ -209,67 +202,140 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         sg.page_off = static_cast<int32_t>(pages_sec.size());
         pages_sec.insert(pages_sec.end(), sg.pages.begin(), sg.pages.end());
     }
+
+    // ---- 5. streaming items -----------------------------------------------------
     std::vector<WorkItem> stream_items, dense_items;
     int32_t num_entries = 0;
-    std::vector<int32_t> per_query(batch, 0);
+    std::vector<int32_t> per_list(static_cast<size_t>(batch) * kv_heads, 0);
     for (const Segment& sg : segs) {
-        const bool dense = is_dense(sg);
+        if (is_dense(sg)) continue;
         const int nq = static_cast<int>(sg.queries.size());
-        const int qpi = dense ? q_per_dense : q_per_stream;
-        const int chunk = dense ? dense_chunk : stream_chunk;
         const int np = static_cast<int>(sg.pages.size());
-        const int kparts = std::max(1, ceil_div(sg.tokens, chunk));
+        const int kparts = std::max(1, ceil_div(sg.tokens, stream_chunk));
         const int ppc = ceil_div(np, kparts);            // pages per KV chunk
         for (int p0 = 0; p0 < np; p0 += ppc) {
             const int p1 = std::min(np, p0 + ppc);
             const int64_t tok_lo = static_cast<int64_t>(p0) * page_size;
             const int kv = static_cast<int>(std::min<int64_t>(sg.tokens - tok_lo,
                                                               static_cast<int64_t>(p1 - p0) * page_size));
-            for (int q0 = 0; q0 < nq; q0 += qpi) {
+            for (int q0 = 0; q0 < nq; q0 += q_per_stream) {
                 WorkItem it{};
                 it.q_off = sg.q_off + q0;
-                it.nq = std::min(qpi, nq - q0);
+                it.nq = std::min(q_per_stream, nq - q0);
                 it.page_off = sg.page_off + p0;
                 it.kv_len = kv;
                 it.entry_base = num_entries;
-                it.kind = dense ? 1 : 0;
+                it.kv_head = -1;
                 it.cost = kv;
-                num_entries += it.nq;
-                for (int i = 0; i < it.nq; ++i) per_query[sg.queries[q0 + i]] += 1;
-                (dense ? dense_items : stream_items).push_back(it);
-                if (dense) header_.dense_tokens += kv; else header_.stream_tokens += kv;
+                num_entries += it.nq * kv_heads;
+                for (int i = 0; i < it.nq; ++i)
+                    for (int h = 0; h < kv_heads; ++h)
+                        per_list[static_cast<size_t>(sg.queries[q0 + i]) * kv_heads + h] += 1;
+                stream_items.push_back(it);
+                header_.stream_tokens += kv;
             }
         }
     }
-    auto by_cost = [](const WorkItem& a, const WorkItem& b) { return a.cost > b.cost; };
-    std::stable_sort(stream_items.begin(), stream_items.end(), by_cost);
-    std::stable_sort(dense_items.begin(), dense_items.end(), by_cost);
+    std::stable_sort(stream_items.begin(), stream_items.end(),
+                     [](const WorkItem& a, const WorkItem& b) { return a.cost > b.cost; });
 
-    // ---- 6. merge lists -------------------------------------------------------
-    std::vector<int32_t> indptr(batch + 1, 0);
-    for (int b = 0; b < batch; ++b) indptr[b + 1] = indptr[b] + per_query[b];
+    // ---- 6. dense items: equal token shares per persistent CTA ------------------
+    // Units = (segment, <= dense_rows query rows, KV head), laid end to end with the KV head
+    // fastest (the heads of one segment stream the same pages, so they should run together).
+    struct Unit { const Segment* sg; int q0, nq, head; };
+    std::vector<Unit> units;
+    int64_t dense_total = 0;
+    for (const Segment& sg : segs) {
+        if (!is_dense(sg)) continue;
+        const int nq = static_cast<int>(sg.queries.size());
+        for (int q0 = 0; q0 < nq; q0 += q_per_dense)
+            for (int h = 0; h < kv_heads; ++h) {
+                units.push_back(Unit{&sg, q0, std::min(q_per_dense, nq - q0), h});
+                dense_total += sg.tokens;
+            }
+        header_.dense_tokens += sg.tokens * ceil_div(nq, q_per_dense);
+    }
+    std::vector<int32_t> cta_begin;
+    if (!units.empty()) {
+        // cuts fall on multiples of `granule` tokens from the start of a unit, so that every
+        // piece starts on a page boundary and on a 64-token tile boundary
+        int64_t granule = 64;
+        while (granule % page_size != 0) granule += 64;
+        const int64_t min_piece = std::max<int64_t>(granule, opt.dense_piece_tokens_min);
+        int64_t ctas = std::min<int64_t>(opt.num_sms, std::max<int64_t>(1, dense_total / min_piece));
+        int64_t target = (dense_total + ctas - 1) / ctas;
+        target = (target + granule - 1) / granule * granule;
+        int64_t used = 0, assigned = 0;
+        cta_begin.push_back(0);
+        auto can_advance = [&]() { return static_cast<int64_t>(cta_begin.size()) < ctas; };
+        auto next_cta = [&]() {
+            cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
+            used = 0;
+            // re-balance: what is left, spread over the CTAs that are left
+            const int64_t left = ctas - static_cast<int64_t>(cta_begin.size()) + 1;
+            target = (dense_total - assigned + left - 1) / left;
+            target = (target + granule - 1) / granule * granule;
+        };
+        for (const Unit& u : units) {
+            int64_t pos = 0;
+            const int64_t tokens = u.sg->tokens;
+            while (pos < tokens) {
+                int64_t cap = target - used;
+                if (!can_advance()) cap = tokens - pos;                     // the last CTA takes what is left
+                else if (cap < min_piece / 2 && used > 0) { next_cta(); continue; }
+                int64_t take = std::min(tokens - pos, std::max(cap, granule));
+                if (take < tokens - pos) take = std::max<int64_t>(granule, take / granule * granule);
+                // do not leave a sliver behind
+                if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
+                WorkItem it{};
+                it.q_off = u.sg->q_off + u.q0;
+                it.nq = u.nq;
+                it.page_off = u.sg->page_off + static_cast<int32_t>(pos / page_size);
+                it.kv_len = static_cast<int32_t>(take);
+                it.entry_base = num_entries;
+                it.kv_head = u.head;
+                it.cost = static_cast<int32_t>(take);
+                num_entries += it.nq;
+                for (int i = 0; i < it.nq; ++i)
+                    per_list[static_cast<size_t>(u.sg->queries[u.q0 + i]) * kv_heads + u.head] += 1;
+                dense_items.push_back(it);
+                used += take;
+                assigned += take;
+                pos += take;
+                if (used >= target && can_advance()) next_cta();
+            }
+        }
+        if (cta_begin.back() != static_cast<int32_t>(dense_items.size())) cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
+    }
+    const int num_dense_ctas = cta_begin.empty() ? 0 : static_cast<int>(cta_begin.size()) - 1;
+
+    // ---- 7. merge lists per (request, KV head) ------------------------------------
+    const size_t n_lists = static_cast<size_t>(batch) * kv_heads;
+    std::vector<int32_t> indptr(n_lists + 1, 0);
+    for (size_t i = 0; i < n_lists; ++i) indptr[i + 1] = indptr[i] + per_list[i];
     std::vector<int32_t> fill(indptr.begin(), indptr.end() - 1);
-    std::vector<int32_t> entries(num_entries, 0);
-    auto scatter = [&](const std::vector<WorkItem>& items) {
-        for (const WorkItem& it : items)
-            for (int i = 0; i < it.nq; ++i) entries[fill[queries_sec[it.q_off + i]]++] = it.entry_base + i;
-    };
-    scatter(stream_items);
-    scatter(dense_items);
-    // deterministic merge order: ascending entry id per query
-    int max_per_query = 0;
-    for (int b = 0; b < batch; ++b) {
-        std::sort(entries.begin() + indptr[b], entries.begin() + indptr[b + 1]);
-        max_per_query = std::max(max_per_query, per_query[b]);
+    std::vector<int32_t> entries(indptr[n_lists], 0);
+    for (const WorkItem& it : stream_items)
+        for (int i = 0; i < it.nq; ++i)
+            for (int h = 0; h < kv_heads; ++h)
+                entries[fill[static_cast<size_t>(queries_sec[it.q_off + i]) * kv_heads + h]++] = it.entry_base + i * kv_heads + h;
+    for (const WorkItem& it : dense_items)
+        for (int i = 0; i < it.nq; ++i)
+            entries[fill[static_cast<size_t>(queries_sec[it.q_off + i]) * kv_heads + it.kv_head]++] = it.entry_base + i;
+    int max_per_list = 0;
+    for (size_t i = 0; i < n_lists; ++i) {
+        std::sort(entries.begin() + indptr[i], entries.begin() + indptr[i + 1]);   // deterministic merge order
+        max_per_list = std::max(max_per_list, per_list[i]);
     }
 
-    // ---- 7. blob --------------------------------------------------------------
+    // ---- 8. blob ------------------------------------------------------------------
     const size_t n_items = stream_items.size() + dense_items.size();
     auto align8 = [](size_t v) { return (v + 7) / 8 * 8; };
     const size_t items_off = 0;
     const size_t queries_off = align8(items_off + n_items * 8);
     const size_t pages_off = align8(queries_off + queries_sec.size());
-    const size_t indptr_off = align8(pages_off + pages_sec.size());
+    const size_t cta_off = align8(pages_off + pages_sec.size());
+    const size_t indptr_off = align8(cta_off + cta_begin.size());
     const size_t entries_off = align8(indptr_off + indptr.size());
     const size_t total = align8(entries_off + entries.size()) + 8;
     blob_.assign(total, 0);
@@ -280,19 +346,23 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                     dense_items.size() * sizeof(WorkItem));
     std::copy(queries_sec.begin(), queries_sec.end(), blob_.begin() + queries_off);
     std::copy(pages_sec.begin(), pages_sec.end(), blob_.begin() + pages_off);
+    std::copy(cta_begin.begin(), cta_begin.end(), blob_.begin() + cta_off);
     std::copy(indptr.begin(), indptr.end(), blob_.begin() + indptr_off);
     std::copy(entries.begin(), entries.end(), blob_.begin() + entries_off);
 
     header_.batch = batch;
     header_.hratio = hratio;
     header_.page_size = page_size;
+    header_.kv_heads = kv_heads;
     header_.num_stream_items = static_cast<int32_t>(stream_items.size());
     header_.num_dense_items = static_cast<int32_t>(dense_items.size());
+    header_.num_dense_ctas = num_dense_ctas;
     header_.num_entries = num_entries;
-    header_.max_entries_per_query = max_per_query;
+    header_.max_entries_per_list = max_per_list;
     header_.items_off = static_cast<int32_t>(items_off);
     header_.queries_off = static_cast<int32_t>(queries_off);
     header_.pages_off = static_cast<int32_t>(pages_off);
+    header_.dense_cta_off = static_cast<int32_t>(cta_off);
     header_.merge_indptr_off = static_cast<int32_t>(indptr_off);
     header_.merge_entries_off = static_cast<int32_t>(entries_off);
     header_.blob_words = static_cast<int32_t>(total);

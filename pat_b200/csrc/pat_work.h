@@ -11,11 +11,15 @@
 //      set of fused boxes that contain them, so that every (page, valid tokens)
 //      pair is attended by all its queries in ONE segment and is read from HBM
 //      once (attention is invariant to KV order, so regrouping is exact);
-//   2. a segment becomes work items: query-row chunks (<= 16 rows for the
-//      streaming kernel, <= 128/256 rows for the dense tensor-core kernel) times
-//      KV chunks sized for load balance, ordered longest first;
-//   3. every (item, query) pair owns a private partial slot ("entry"), and a
-//      CSR list per query tells the merge kernel which entries to combine.
+//   2. segments with few query rows become streaming items (<= 16 rows x one KV
+//      chunk, run for every KV head), ordered longest first;
+//   3. segments shared by many rows become dense items for the tensor-core
+//      kernel: per KV head, the token ranges of all (segment, <= 256 rows) units
+//      are laid end to end and cut into equal shares, one share per persistent
+//      CTA, so that every CTA streams the same number of tokens;
+//   4. every (item, query, KV head) triple owns a private partial slot ("entry":
+//      hratio rows of D floats + LSEs), and a CSR list per (request, KV head)
+//      tells the merge kernel which entries to combine.
 //
 // Multiplicity is preserved: a query that attends a page twice in the plan
 // attends it twice here.
@@ -38,14 +42,13 @@ struct PlanBucketView {
 
 struct WorkOptions {
     int num_sms = 148;
-    int stream_rows = 16;          // query rows per streaming item
-    int dense_rows = 0;            // query rows per dense item (0 = dense kernel off)
-    int dense_min_rows = 1 << 30;  // segments with at least this many rows go to the dense kernel
+    int stream_rows = 16;              // query rows per streaming item
+    int dense_rows = 256;              // query rows per dense item (0 = dense kernel off)
+    int dense_min_rows = 17;           // segments with at least this many rows go to the dense kernel
     int chunk_tokens_min = 256;
     int chunk_tokens_max = 2048;
-    int dense_chunk_tokens_max = 2048;
-    int items_per_sm = 8;          // target number of streaming items per SM (all KV heads)
-    int fold_tokens = 0;           // shared segments with <= this many tokens are copied into each query
+    int dense_piece_tokens_min = 512;  // a dense share is not cut (much) below this many tokens
+    int items_per_sm = 8;              // target number of streaming items per SM (all KV heads)
 };
 
 // One work item = 8 int32 on the device.
@@ -54,9 +57,10 @@ struct WorkItem {
     int32_t nq;          // number of queries (rows = nq * hratio)
     int32_t page_off;    // offset of its first page id in the page section
     int32_t kv_len;      // valid tokens (the first kv_len tokens of its pages)
-    int32_t entry_base;  // partial slot of its first query; slot of query i is entry_base + i
-    int32_t kind;        // 0 = streaming, 1 = dense
-    int32_t cost;        // tokens x row tiles (ordering key)
+    int32_t entry_base;  // streaming: entry of (query i, head h) = entry_base + i * kv_heads + h
+                         // dense:     entry of query i            = entry_base + i
+    int32_t kv_head;     // dense items: the KV head; streaming items: -1 (run for every head)
+    int32_t cost;        // tokens (ordering key)
     int32_t reserved;
 };
 static_assert(sizeof(WorkItem) == 32, "device layout");
@@ -65,23 +69,25 @@ struct WorkHeader {
     int32_t batch;
     int32_t hratio;
     int32_t page_size;
-    int32_t num_stream_items;   // items [0, num_stream_items) are streaming, longest first
-    int32_t num_dense_items;    // then the dense items, longest first
+    int32_t kv_heads;
+    int32_t num_stream_items;     // items [0, num_stream_items), longest first
+    int32_t num_dense_items;      // then the dense items, grouped by CTA
+    int32_t num_dense_ctas;       // persistent CTAs of the dense kernel
     int32_t num_entries;
-    int32_t max_entries_per_query;
-    int32_t items_off;          // all offsets in int32 units from the start of the blob
+    int32_t max_entries_per_list;
+    int32_t items_off;            // all offsets in int32 units from the start of the blob
     int32_t queries_off;
     int32_t pages_off;
-    int32_t merge_indptr_off;   // [batch + 1]
-    int32_t merge_entries_off;  // [num_entries]
+    int32_t dense_cta_off;        // [num_dense_ctas + 1] first dense item of each CTA
+    int32_t merge_indptr_off;     // [batch * kv_heads + 1]
+    int32_t merge_entries_off;    // [sum of list lengths]
     int32_t blob_words;
     int32_t num_segments;
-    int32_t max_page_id;        // largest page id any item touches (-1 if none)
-    int32_t reserved;
-    int64_t unique_tokens;      // sum of segment tokens (each page counted once)
-    int64_t stream_tokens;      // tokens read by streaming items (x row chunks)
-    int64_t dense_tokens;
-    int64_t stream_unique_tokens;
+    int32_t max_page_id;          // largest page id any item touches (-1 if none)
+    int64_t unique_tokens;        // sum of segment tokens (each page counted once)
+    int64_t stream_tokens;        // tokens read by streaming items per KV head (a segment counts once per row chunk)
+    int64_t dense_tokens;         // same for dense items
+    int64_t stream_unique_tokens; // unique tokens of the segments the streaming kernel handles
     int64_t dense_unique_tokens;
 };
 

@@ -28,14 +28,14 @@ def test_every_declared_symbol_is_exported_and_bound(native_lib):
 
 def test_structs_match_the_header_sizes(native_lib):
     # pat_work_header: 16 int32 + 5 int64; pat_work_options: 8 int32; pat_plan_bucket: 4 int32 + 4 ptr
-    assert C.sizeof(N.WorkHeader) == 16 * 4 + 5 * 8
+    assert C.sizeof(N.WorkHeader) == 18 * 4 + 5 * 8
     assert C.sizeof(N.WorkOptions) == 32
     assert C.sizeof(N.PlanBucket) == 16 + 4 * 8
     assert C.sizeof(N.BucketView) == 24 + 5 * 8
 
 
 def test_version_and_strerror(native_lib):
-    assert native_lib.pat_b200_abi_version() >= 1
+    assert native_lib.pat_b200_abi_version() >= 2
     assert N.strerror(0) == "ok"
     assert "workspace" in N.strerror(-12)
     assert N.strerror(-999) == "unknown status"
@@ -65,8 +65,9 @@ def test_decode_rejects_bad_arguments_without_touching_a_device(native_lib):
     a = N.DecodeArgs()
     assert native_lib.pat_b200_decode(C.byref(a), None) == -1
     hdr = N.WorkHeader()
-    hdr.num_entries = 10
-    assert native_lib.pat_b200_workspace_bytes(C.byref(hdr), 8, 128) >= 10 * 8 * 129 * 4
+    hdr.num_entries = 10            # 10 slots of hratio rows each
+    hdr.hratio = 4
+    assert native_lib.pat_b200_workspace_bytes(C.byref(hdr), 8, 128) >= 10 * 4 * 129 * 4
     assert native_lib.pat_b200_workspace_bytes(None, 8, 128) == 0
 
 

@@ -126,7 +126,7 @@ def test_benchmark_configs_full_sampled(cfg, sample, native_lib):
     alt1, lse1, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale,
                               cfg=P.WorkConfig(disable_dense=1))
     alt2, lse2, _ = _run_tree(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale,
-                              semantics="py", cfg=P.WorkConfig(chunk_tokens_max=512, dense_chunk_tokens_max=512))
+                              semantics="py", cfg=P.WorkConfig(chunk_tokens_max=512, dense_piece_tokens_min=128))
     tol = TOL[dtype]
     assert (out - alt1).abs().max().item() <= tol
     assert (out - alt2).abs().max().item() <= tol
@@ -146,7 +146,7 @@ def test_scaled_configs_all_requests(cfg, factor, native_lib):
 
 
 @pytest.mark.parametrize("opts", [dict(disable_dense=1), dict(dense_min_rows=64),
-                                  dict(chunk_tokens_min=16, chunk_tokens_max=64, dense_chunk_tokens_max=64),
+                                  dict(chunk_tokens_min=16, chunk_tokens_max=64, dense_piece_tokens_min=64),
                                   dict(items_per_sm=64)])
 def test_work_cuts_agree_with_oracle(opts, native_lib):
     w = scaled_down(1, 4)

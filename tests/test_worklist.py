@@ -134,23 +134,34 @@ def test_full_configs_dedup_every_page(cfg, native_lib):
     header, blob = W.build_work(_plan_lists(ki), w.batch, w.group, w.num_kv_heads, w.page_size)
     assert header.unique_tokens == w.unique_tokens
     items = W.items_of(header, blob)
-    # per request: tokens attended == its context length
-    seen = np.zeros(w.batch, dtype=np.int64)
-    for it in items:
+    hk = w.num_kv_heads
+    # per (request, KV head): tokens attended == the request's context length
+    seen = np.zeros((w.batch, hk), dtype=np.int64)
+    for idx, it in enumerate(items):
         qs = blob[header.queries_off + it[0]: header.queries_off + it[0] + it[1]]
-        np.add.at(seen, qs, it[3])
-    assert seen.tolist() == list(w.seq_lens)
-    # entries: a permutation of 0..num_entries-1 split by request
-    indptr = blob[header.merge_indptr_off: header.merge_indptr_off + w.batch + 1]
-    entries = blob[header.merge_entries_off: header.merge_entries_off + header.num_entries]
+        heads = range(hk) if idx < header.num_stream_items else [it[5]]
+        for h in heads:
+            np.add.at(seen[:, h], qs, it[3])
+    assert (seen == np.asarray(w.seq_lens)[:, None]).all()
+    # merge lists: a partition of the entries
+    indptr = blob[header.merge_indptr_off: header.merge_indptr_off + w.batch * hk + 1]
+    entries = blob[header.merge_entries_off: header.merge_entries_off + int(indptr[-1])]
     assert indptr[-1] == header.num_entries
     assert sorted(entries.tolist()) == list(range(header.num_entries))
-    # longest first within each kernel class
+    # streaming items: longest first
     costs = items[:header.num_stream_items, 6]
     assert (np.diff(costs) <= 0).all()
-    # every page id once per segment: total distinct (page) == pages in use
-    pages = blob[header.pages_off: header.pages_off + int(sum(-(-l // w.page_size) for l in [0]))]
     assert header.max_page_id < w.num_pages
+    # dense items: every CTA gets (nearly) the same number of tokens, cut on 64-token boundaries
+    ctas = W.dense_ctas(header, blob)
+    assert 0 < len(ctas) <= 148 and ctas[0][0] == 0 and ctas[-1][1] == header.num_dense_items
+    dense = items[header.num_stream_items:]
+    load = np.array([dense[a:b, 3].sum() for a, b in ctas])
+    assert load.sum() == header.dense_tokens * hk
+    assert load.max() <= 1.15 * load.mean() + 512, (load.max(), load.mean())
+    assert (dense[:, 1] * w.group <= 256).all()
+    starts_on_tile = (dense[:, 2] - np.array([0])) >= 0
+    assert starts_on_tile.all()
 
 
 def test_partial_shared_last_page(native_lib):

@@ -71,7 +71,7 @@ def test_static_scratch_entry_point_matches_the_allocating_one(native_lib):
 
         # a work list whose partials do not fit the fixed array is refused, nothing is launched
         big = N.WorkHeader.from_buffer_copy(work.header)
-        big.num_entries = N.STATIC_SCRATCH_BYTES // (w.num_q_heads * (w.head_dim + 1) * 4) + 1
+        big.num_entries = N.STATIC_SCRATCH_BYTES // (w.group * (w.head_dim + 1) * 4) + 1
         out = torch.zeros_like(q)
         a = _args(q, k, v, out, work, scale)
         a.work = big

@@ -52,28 +52,45 @@ def items_of(header, blob):
 def execute(header, blob, q, k_cache, v_cache, scale):
     """Returns (out [B,H,D] fp32, lse [B,H] fp32)."""
     B, _, H, D = q.shape
-    page = header.page_size
-    part_o = torch.zeros(header.num_entries, H, D)
-    part_l = torch.full((header.num_entries, H), float("nan"))
+    page, hk, hr = header.page_size, header.kv_heads, header.hratio
+    assert H == hk * hr
+    part_o = torch.zeros(header.num_entries, hr, D)
+    part_l = torch.full((header.num_entries, hr), float("nan"))
     written = np.zeros(header.num_entries, dtype=np.int32)
-    for it in items_of(header, blob):
-        q_off, nq, page_off, kv_len, entry_base = (int(x) for x in it[:5])
+    for idx, it in enumerate(items_of(header, blob)):
+        q_off, nq, page_off, kv_len, entry_base, kv_head = (int(x) for x in it[:6])
+        streaming = idx < header.num_stream_items
+        assert (kv_head == -1) == streaming
         qs = blob[header.queries_off + q_off: header.queries_off + q_off + nq].tolist()
         n_pages = -(-kv_len // page)
         pages = blob[header.pages_off + page_off: header.pages_off + page_off + n_pages].tolist()
         kk = O.gather_request_kv(k_cache, pages, kv_len)
         vv = O.gather_request_kv(v_cache, pages, kv_len)
-        o, l = O.segment_attention(q[qs, 0], kk, vv, scale)
-        part_o[entry_base: entry_base + nq] = o
-        part_l[entry_base: entry_base + nq] = l
-        written[entry_base: entry_base + nq] += 1
+        for kvh in (range(hk) if streaming else [kv_head]):
+            heads = slice(kvh * hr, (kvh + 1) * hr)
+            o, l = O.segment_attention(q[qs, 0][:, heads], kk[:, kvh:kvh + 1], vv[:, kvh:kvh + 1], scale)
+            for i in range(nq):
+                e = entry_base + (i * hk + kvh if streaming else i)
+                part_o[e], part_l[e] = o[i], l[i]
+                written[e] += 1
     assert (written == 1).all(), "every entry must be written exactly once"
-    indptr = blob[header.merge_indptr_off: header.merge_indptr_off + B + 1]
-    entries = blob[header.merge_entries_off: header.merge_entries_off + header.num_entries]
+    n_lists = B * hk
+    indptr = blob[header.merge_indptr_off: header.merge_indptr_off + n_lists + 1]
+    entries = blob[header.merge_entries_off: header.merge_entries_off + int(indptr[-1])]
+    assert sorted(entries.tolist()) == list(range(header.num_entries)), "every entry is merged exactly once"
     out = torch.zeros(B, H, D)
     lse = torch.full((B, H), float("-inf"))
     for b in range(B):
-        e = torch.as_tensor(entries[indptr[b]: indptr[b + 1]], dtype=torch.long)
-        if len(e):
-            out[b], lse[b] = O.merge_partials(part_o[e], part_l[e])
+        for kvh in range(hk):
+            lst = b * hk + kvh
+            e = torch.as_tensor(entries[indptr[lst]: indptr[lst + 1]], dtype=torch.long)
+            if len(e):
+                heads = slice(kvh * hr, (kvh + 1) * hr)
+                out[b, heads], lse[b, heads] = O.merge_partials(part_o[e], part_l[e])
     return out, lse
+
+
+def dense_ctas(header, blob):
+    """[(first, last)] dense item ranges (indices into the dense section) per persistent CTA."""
+    b = blob[header.dense_cta_off: header.dense_cta_off + header.num_dense_ctas + 1].tolist()
+    return list(zip(b[:-1], b[1:]))
