@@ -9,13 +9,15 @@
 //   warps 0-3 / 4-7: softmax groups 0 / 1.  Thread r of group w owns query row 128 w + r
 //            (= TMEM lane r).  Per 64-token tile it reads its row of S = Q K^T from TMEM
 //            (tcgen05.ld), does the online softmax without any cross-thread traffic and writes
-//            P (bf16/fp16) to shared memory; at the end of an item it reads O from TMEM and
-//            stores the normalised fp32 partial and its LSE.
-//   warp 8:  TMA producer: 4 stages of 64 tokens (K and V boxes of 16 tokens x 64 elements,
+//            P (bf16/fp16 pairs) back into TMEM over the S columns it has just consumed
+//            (tcgen05.st); at the end of an item it reads O from TMEM and stores the
+//            normalised fp32 partial and its LSE.
+//   warp 8:  TMA producer: 5 stages of 64 tokens (K and V boxes of 16 tokens x 64 elements,
 //            128-byte swizzle - the layout the UMMA shared-memory descriptors describe).
-//   warp 9:  one thread issues every MMA: S_w(j+1) = Q_w K^T (M128 N64 K16 x D/16) one tile
-//            ahead of the softmax, then O_w += P_w(j) V (M128 N=D K16 x 4); completion is
-//            signalled with tcgen05.commit on mbarriers.
+//   warp 9:  one thread issues every MMA: S_w(j) = Q_w K_j^T (M128 N64 K16 x D/16, operands
+//            from shared memory) two tiles ahead of the softmax, and O_w += P_w(j) V_j (M128
+//            N=D K16 x 4, A = P from TMEM, B = V from shared memory); completion is signalled
+//            with tcgen05.commit on mbarriers.
 //
 // Both row tiles share the staged K/V tile, so a shared page is read from HBM (and from L2)
 // once per 256 query rows.  TMEM (512 columns): S double-buffered per group (4 x 64) + O per
@@ -30,7 +32,7 @@
 namespace pat {
 
 constexpr int kTcTile = 64;                 // tokens per tile
-constexpr int kTcStages = 4;
+constexpr int kTcStages = 5;
 constexpr int kTcThreads = 320;
 constexpr int kTcTmemCols = 512;
 constexpr float kTcLazyLog2 = 8.0f;
@@ -40,10 +42,8 @@ template <int D> struct TcSmem {
     static constexpr int kQBytes = kBoxes * 128 * 128;          // per row tile: [box][128 rows][128 B]
     static constexpr int kKBytes = kBoxes * kTcTile * 128;      // [box][64 tokens][128 B]
     static constexpr int kStageBytes = 2 * kKBytes;             // K then V
-    static constexpr int kPBytes = 128 * 128;                   // per row tile: [128 rows][64 tokens x 2 B]
     static constexpr int kQOff = 0;
-    static constexpr int kPOff = kQOff + 2 * kQBytes;
-    static constexpr int kStageOff = kPOff + 2 * kPBytes;
+    static constexpr int kStageOff = kQOff + 2 * kQBytes;
     static constexpr int kBarOff = kStageOff + kTcStages * kStageBytes;
     static constexpr int kRequest = kBarOff + 256;              // 17 mbarriers + tmem base word + flag
 };
@@ -71,6 +71,31 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+          "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // 64 consecutive fp32 columns of this thread's TMEM lane
@@ -162,13 +187,13 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         if (tid == 0 && p.status) atomicExch(p.status, 10);
         return;
     }
-    const uint32_t sQ = base + L::kQOff, sP = base + L::kPOff, sStage = base + L::kStageOff;
+    const uint32_t sQ = base + L::kQOff, sStage = base + L::kStageOff;
     const uint32_t bars = base + L::kBarOff;
-    // barrier map (8 bytes each): full[4] empty[4] s_full[w][b] (4) p_ready[2] o_done[2] q_ready
-    const uint32_t bar_full = bars, bar_empty = bars + 32, bar_s = bars + 64, bar_p = bars + 96, bar_o = bars + 112,
-                   bar_q = bars + 128;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 144);
-    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 152);
+    // barrier map (8 bytes each): full[5] empty[5] s_full[w][b] (4) p_ready[2] o_done[2] q_ready
+    const uint32_t bar_full = bars, bar_empty = bars + 40, bar_s = bars + 80, bar_p = bars + 112, bar_o = bars + 128,
+                   bar_q = bars + 144;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 160);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 168);
 
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
     if (tid == 0) *poisoned = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
@@ -180,7 +205,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
-        for (int i = 0; i < 8; ++i) mbar_init(bar_full + 8 * i, 1);    // full[4], empty[4]
+        for (int i = 0; i < 2 * kTcStages; ++i) mbar_init(bar_full + 8 * i, 1);   // full[], empty[]
         for (int i = 0; i < 4; ++i) mbar_init(bar_s + 8 * i, 1);       // s_full
         for (int i = 0; i < 2; ++i) mbar_init(bar_p + 8 * i, 128);     // p_ready: every thread of a group
         for (int i = 0; i < 2; ++i) mbar_init(bar_o + 8 * i, 1);       // o_done
@@ -244,42 +269,53 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
             tc_fence_after();
 
-            auto issue_qk = [&](int j) {
+            const int nw = two ? 2 : 1;
+            auto wait_stage = [&](int j) {
                 const int s = (g + j) % kTcStages;
                 if (ok) ok = mbar_wait(bar_full + 8 * s, ((g + j) / kTcStages) & 1);
                 tc_fence_after();
-                const uint32_t k_addr = sStage + s * L::kStageBytes;
-                for (int w = 0; w < (two ? 2 : 1); ++w) {
-                    const int t = (w == 0 ? g : g1) + j;               // this group's running tile index
-                    const uint32_t d_tmem = tmem_base + w * 128 + (t & 1) * kTcTile;
+            };
+            auto issue_qk = [&](int w, int j) {                        // S_w = Q_w K_j^T into buffer (t & 1)
+                const int t = (w == 0 ? g : g1) + j;                   // this group's running tile index
+                const uint32_t k_addr = sStage + ((g + j) % kTcStages) * L::kStageBytes;
+                const uint32_t d_tmem = tmem_base + w * 128 + (t & 1) * kTcTile;
 #pragma unroll
-                    for (int ks = 0; ks < D / 16; ++ks) {
-                        const uint64_t a = umma_desc_kmajor(sQ + w * L::kQBytes + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
-                        const uint64_t b = umma_desc_kmajor(k_addr + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
-                        tc_mma(d_tmem, a, b, idesc_qk, ks > 0 ? 1u : 0u);
-                    }
-                    tc_commit(bar_s + 8 * (2 * w + (t & 1)));
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t a = umma_desc_kmajor(sQ + w * L::kQBytes + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
+                    const uint64_t b = umma_desc_kmajor(k_addr + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
+                    tc_mma(d_tmem, a, b, idesc_qk, ks > 0 ? 1u : 0u);
                 }
+                tc_commit(bar_s + 8 * (2 * w + (t & 1)));
             };
 
-            issue_qk(0);
+            wait_stage(0);
+            for (int w = 0; w < nw; ++w) issue_qk(w, 0);
+            if (n_tiles > 1) {
+                wait_stage(1);
+                for (int w = 0; w < nw; ++w) issue_qk(w, 1);
+            }
             for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) issue_qk(j + 1);
                 const int s = (g + j) % kTcStages;
                 const uint32_t v_addr = sStage + s * L::kStageBytes + L::kKBytes;
-                for (int w = 0; w < (two ? 2 : 1); ++w) {
+                for (int w = 0; w < nw; ++w) {
                     const int t = (w == 0 ? g : g1) + j;
-                    if (ok) ok = mbar_wait(bar_p + 8 * w, t & 1);      // P_w(j) written, S_w(j) consumed
+                    if (ok) ok = mbar_wait(bar_p + 8 * w, t & 1);      // P_w(j) is in TMEM (over S_w(j))
                     tc_fence_after();
+                    const uint32_t p_tmem = tmem_base + w * 128 + (t & 1) * kTcTile;
 #pragma unroll
                     for (int ks = 0; ks < kTcTile / 16; ++ks) {
-                        const uint64_t a = umma_desc_kmajor(sP + w * L::kPBytes + ks * 32);
                         const uint64_t b = umma_desc_mnmajor(v_addr + ks * 2048, kTcTile * 128);
-                        tc_mma(tmem_base + 256 + w * 128, a, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                        tc_mma_ts(tmem_base + 256 + w * 128, p_tmem + ks * 8, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_o + 8 * w);
+                    // the S/P buffer of tile j is free again once the product above has read it
+                    // (MMAs execute in issue order): compute S two tiles ahead into it
+                    if (j + 2 < n_tiles) {
+                        if (w == 0) wait_stage(j + 2);
+                        issue_qk(w, j + 2);
+                    }
                 }
-                tc_commit(bar_empty + 8 * s);                           // K/V stage free when both are done
+                tc_commit(bar_empty + 8 * s);                           // K/V stage free when everything above is done
             }
             g += n_tiles;
             if (two) g1 += n_tiles;
@@ -356,11 +392,13 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             }
             const float mx = fmaxf(mx0, mx1);
 
-            // the previous PV of this group must be done before P is overwritten or O is rescaled
-            if (j > 0 && ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
-            tc_fence_after();
+            bool o_waited = false;
             const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
             if (j > 0 && __any_sync(kFullMask, raise)) {
+                // O may only be touched once every earlier P V of this group has completed
+                if (ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
+                tc_fence_after();
+                o_waited = true;
                 const float alpha = raise ? fast_exp2((m_used - mx) * c) : 1.f;
                 l *= alpha;
 #pragma unroll 1
@@ -385,12 +423,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 packed[i] = Elt<T>::pack(p0, p1);
             }
             l += sum0 + sum1;
-#pragma unroll
-            for (int k8 = 0; k8 < 8; ++k8) {   // row r of P: 8 chunks of 16 B, swizzled like a [128 x 128 B] tile
-                const uint32_t dst = sP + w * L::kPBytes + swz128(r, k8);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * k8]), "r"(packed[4 * k8 + 1]),
-                             "r"(packed[4 * k8 + 2]), "r"(packed[4 * k8 + 3]) : "memory");
-            }
+            // P over the first 32 columns of the S buffer this thread has just read (its own lane)
+            tmem_st32(tmem_s + (t & 1) * kTcTile, packed);
             if (valid < kTcTile && w == 0) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them so that P = 0 times garbage cannot make a NaN.  The stage has landed
@@ -406,8 +440,11 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                     const uint32_t dst = sStage + s * L::kStageBytes + L::kKBytes + b * (kTcTile * 128) + vrow * 128 + ((rem & 7) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
                 }
+                fence_async_smem();
             }
-            fence_async_smem();
+            // consume the o_done phase of the previous tile (issued a whole tile ago, so this does
+            // not stall); every phase is waited for exactly once, which keeps the parities in step
+            if (j > 0 && !o_waited && ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
             tc_fence_before();
             mbar_arrive(bar_p + 8 * w);
         }

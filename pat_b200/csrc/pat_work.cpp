@@ -240,72 +240,84 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                      [](const WorkItem& a, const WorkItem& b) { return a.cost > b.cost; });
 
     // ---- 6. dense items: equal token shares per persistent CTA ------------------
-    // Units = (segment, <= dense_rows query rows, KV head), laid end to end with the KV head
-    // fastest (the heads of one segment stream the same pages, so they should run together).
-    struct Unit { const Segment* sg; int q0, nq, head; };
-    std::vector<Unit> units;
-    int64_t dense_total = 0;
+    // Columns = (segment, <= dense_rows query rows); their token ranges are laid end to end
+    // and cut into `shares` equal parts.  Share s is executed by kv_heads CTAs, one per KV
+    // head (CTA id = s * kv_heads + head): the heads of a share walk the same pages at the
+    // same time, so every 2 KB cache row (all heads of a token) is fetched within a short
+    // window, as in the streaming kernel.
+    struct Column { const Segment* sg; int q0, nq; };
+    std::vector<Column> columns;
+    int64_t dense_total = 0;       // tokens over all columns (per KV head)
     for (const Segment& sg : segs) {
         if (!is_dense(sg)) continue;
         const int nq = static_cast<int>(sg.queries.size());
-        for (int q0 = 0; q0 < nq; q0 += q_per_dense)
-            for (int h = 0; h < kv_heads; ++h) {
-                units.push_back(Unit{&sg, q0, std::min(q_per_dense, nq - q0), h});
-                dense_total += sg.tokens;
-            }
-        header_.dense_tokens += sg.tokens * ceil_div(nq, q_per_dense);
+        for (int q0 = 0; q0 < nq; q0 += q_per_dense) {
+            columns.push_back(Column{&sg, q0, std::min(q_per_dense, nq - q0)});
+            dense_total += sg.tokens;
+        }
     }
+    header_.dense_tokens = dense_total;
     std::vector<int32_t> cta_begin;
-    if (!units.empty()) {
-        // cuts fall on multiples of `granule` tokens from the start of a unit, so that every
+    if (!columns.empty()) {
+        // cuts fall on multiples of `granule` tokens from the start of a column, so that every
         // piece starts on a page boundary and on a 64-token tile boundary
         int64_t granule = 64;
         while (granule % page_size != 0) granule += 64;
         const int64_t min_piece = std::max<int64_t>(granule, opt.dense_piece_tokens_min);
-        int64_t ctas = std::min<int64_t>(opt.num_sms, std::max<int64_t>(1, dense_total / min_piece));
-        int64_t target = (dense_total + ctas - 1) / ctas;
-        target = (target + granule - 1) / granule * granule;
+        const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / kv_heads);
+        const int64_t shares = std::min<int64_t>(max_shares, std::max<int64_t>(1, dense_total / min_piece));
+        struct Piece { const Column* col; int64_t pos, take; };
+        std::vector<std::vector<Piece>> share_pieces(1);
         int64_t used = 0, assigned = 0;
-        cta_begin.push_back(0);
-        auto can_advance = [&]() { return static_cast<int64_t>(cta_begin.size()) < ctas; };
-        auto next_cta = [&]() {
-            cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
+        int64_t target = (dense_total + shares - 1) / shares;
+        target = (target + granule - 1) / granule * granule;
+        auto can_advance = [&]() { return static_cast<int64_t>(share_pieces.size()) < shares; };
+        auto next_share = [&]() {
+            share_pieces.emplace_back();
             used = 0;
-            // re-balance: what is left, spread over the CTAs that are left
-            const int64_t left = ctas - static_cast<int64_t>(cta_begin.size()) + 1;
+            // re-balance: what is left, spread over the shares that are left
+            const int64_t left = shares - static_cast<int64_t>(share_pieces.size()) + 1;
             target = (dense_total - assigned + left - 1) / left;
             target = (target + granule - 1) / granule * granule;
         };
-        for (const Unit& u : units) {
+        for (const Column& col : columns) {
             int64_t pos = 0;
-            const int64_t tokens = u.sg->tokens;
+            const int64_t tokens = col.sg->tokens;
             while (pos < tokens) {
                 int64_t cap = target - used;
-                if (!can_advance()) cap = tokens - pos;                     // the last CTA takes what is left
-                else if (cap < min_piece / 2 && used > 0) { next_cta(); continue; }
+                if (!can_advance()) cap = tokens - pos;                     // the last share takes what is left
+                else if (cap < min_piece / 2 && used > 0) { next_share(); continue; }
                 int64_t take = std::min(tokens - pos, std::max(cap, granule));
                 if (take < tokens - pos) take = std::max<int64_t>(granule, take / granule * granule);
                 // do not leave a sliver behind
                 if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
-                WorkItem it{};
-                it.q_off = u.sg->q_off + u.q0;
-                it.nq = u.nq;
-                it.page_off = u.sg->page_off + static_cast<int32_t>(pos / page_size);
-                it.kv_len = static_cast<int32_t>(take);
-                it.entry_base = num_entries;
-                it.kv_head = u.head;
-                it.cost = static_cast<int32_t>(take);
-                num_entries += it.nq;
-                for (int i = 0; i < it.nq; ++i)
-                    per_list[static_cast<size_t>(u.sg->queries[u.q0 + i]) * kv_heads + u.head] += 1;
-                dense_items.push_back(it);
+                share_pieces.back().push_back(Piece{&col, pos, take});
                 used += take;
                 assigned += take;
                 pos += take;
-                if (used >= target && can_advance()) next_cta();
+                if (used >= target && can_advance() && (pos < tokens || &col != &columns.back())) next_share();
             }
         }
-        if (cta_begin.back() != static_cast<int32_t>(dense_items.size())) cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
+        for (const auto& pieces : share_pieces) {
+            for (int h = 0; h < kv_heads; ++h) {
+                cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
+                for (const Piece& pc : pieces) {
+                    WorkItem it{};
+                    it.q_off = pc.col->sg->q_off + pc.col->q0;
+                    it.nq = pc.col->nq;
+                    it.page_off = pc.col->sg->page_off + static_cast<int32_t>(pc.pos / page_size);
+                    it.kv_len = static_cast<int32_t>(pc.take);
+                    it.entry_base = num_entries;
+                    it.kv_head = h;
+                    it.cost = static_cast<int32_t>(pc.take);
+                    num_entries += it.nq;
+                    for (int i = 0; i < it.nq; ++i)
+                        per_list[static_cast<size_t>(pc.col->sg->queries[pc.col->q0 + i]) * kv_heads + h] += 1;
+                    dense_items.push_back(it);
+                }
+            }
+        }
+        cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
     }
     const int num_dense_ctas = cta_begin.empty() ? 0 : static_cast<int>(cta_begin.size()) - 1;
 
