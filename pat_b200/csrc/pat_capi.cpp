@@ -23,7 +23,7 @@ pat::WorkOptions to_options(const pat_work_options* o) {
     // Defaults: query-row tiles of 16 through the streaming kernel; segments with
     // more than 16 rows go through the dense (tensor-core tile) kernel in tiles of
     // up to 128 rows.
-    w.dense_rows = 256;
+    w.dense_rows = 128;
     w.dense_min_rows = 17;
     if (!o) return w;
     if (o->num_sms > 0) w.num_sms = o->num_sms;

@@ -88,6 +88,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     p.scale = a.softmax_scale;
     p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
     p.status = a.status_word;
+    p.debug = a.flags >> 8;
 
     int launches = 0;
     if (a.work.num_stream_items > 0 && !(a.flags & PAT_SKIP_STREAM)) {

@@ -1,28 +1,31 @@
 // Dense-tile attention on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// Persistent kernel, one CTA per SM.  A CTA walks its share of dense work items (each item:
-// up to 256 query rows - two 128-row tiles - of one KV head over a range of tokens of a
-// shared segment); the shares are cut on the host so that every CTA streams the same number
-// of tokens.  Replaces the reference's M=64 mma.sync tile (csrc/pat_fwd_kernel.h:25-299,
-// csrc/kernel_traits.h:45-123) for segments that many queries share.
+// Persistent kernel, one CTA per SM.  A CTA walks its list of dense work items (each item: up
+// to 128 query rows of one KV head over a range of tokens of a shared segment); the lists are
+// cut on the host so that every CTA streams the same number of tokens, and the CTAs that work
+// on the same tokens (other KV heads, the other 128-row half) run side by side.  Replaces the
+// reference's M=64 mma.sync tile (csrc/pat_fwd_kernel.h:25-299, csrc/kernel_traits.h:45-123)
+// for segments that many queries share.
 //
-//   warps 0-3 / 4-7: softmax groups 0 / 1.  Thread r of group w owns query row 128 w + r
-//            (= TMEM lane r).  Per 64-token tile it reads its row of S = Q K^T from TMEM
-//            (tcgen05.ld), does the online softmax without any cross-thread traffic and writes
-//            P (bf16/fp16 pairs) back into TMEM over the S columns it has just consumed
-//            (tcgen05.st); at the end of an item it reads O from TMEM and stores the
-//            normalised fp32 partial and its LSE.
-//   warp 8:  TMA producer: 5 stages of 64 tokens (K and V boxes of 16 tokens x 64 elements,
-//            128-byte swizzle - the layout the UMMA shared-memory descriptors describe).
-//   warp 9:  one thread issues every MMA: S_w(j) = Q_w K_j^T (M128 N64 K16 x D/16, operands
-//            from shared memory) two tiles ahead of the softmax, and O_w += P_w(j) V_j (M128
-//            N=D K16 x 4, A = P from TMEM, B = V from shared memory); completion is signalled
-//            with tcgen05.commit on mbarriers.
+//   warps 0-3: softmax.  Thread r owns query row r (= TMEM lane r).  Per 64-token tile it reads
+//            its row of S = Q K^T from TMEM (tcgen05.ld), does the online softmax without any
+//            cross-thread traffic and writes P (bf16/fp16 pairs) back into TMEM over the S
+//            columns it has just consumed (tcgen05.st); at the end of an item it reads O from
+//            TMEM and stores the normalised fp32 partial and its LSE.
+//   warp 4 / warp 6: TMA producers for K and for V, rings of 6 tiles of 64 tokens each (boxes of
+//            16 tokens x 64 elements, 128-byte swizzle - the layout the UMMA shared-memory
+//            descriptors describe).  A K tile is released as soon as its S = Q K^T has
+//            completed, a V tile when its P V has.
+//   warp 5:  one thread issues every MMA: S(j) = Q K_j^T (M128 N64 K16 x D/16, both operands
+//            from shared memory) five tiles ahead of the softmax, and O += P(j) V_j (M128 N=D
+//            K16 x 4, A = P from TMEM, B = V from shared memory); completion is signalled with
+//            tcgen05.commit on mbarriers.
 //
-// Both row tiles share the staged K/V tile, so a shared page is read from HBM (and from L2)
-// once per 256 query rows.  TMEM (512 columns): S double-buffered per group (4 x 64) + O per
-// group (2 x D).  The running maximum is only raised when a tile exceeds it by more than 2^8
-// (the offset cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
+// Why so deep: a tcgen05.commit needs of the order of a microsecond to reach its mbarrier, about
+// three times the softmax time of a tile, so S is kept in a ring of six TMEM buffers (6 x 64
+// columns + D columns of O) and no thread ever waits for a product it has just requested.
+// The running maximum is only raised when a tile exceeds it by more than 2^8 (the offset
+// cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
 // Every mbarrier wait is bounded; a wait that gives up records a code in the status word,
 // later waits are skipped and the CTA still frees its TMEM before it returns.
 #pragma once
@@ -32,20 +35,20 @@
 namespace pat {
 
 constexpr int kTcTile = 64;                 // tokens per tile
-constexpr int kTcStages = 5;
-constexpr int kTcThreads = 320;
+constexpr int kTcRing = 6;                  // depth of the K, V and S rings
+constexpr int kTcThreads = 224;
 constexpr int kTcTmemCols = 512;
 constexpr float kTcLazyLog2 = 8.0f;
 
 template <int D> struct TcSmem {
     static constexpr int kBoxes = D / 64;
-    static constexpr int kQBytes = kBoxes * 128 * 128;          // per row tile: [box][128 rows][128 B]
+    static constexpr int kQBytes = kBoxes * 128 * 128;          // [box][128 rows][128 B]
     static constexpr int kKBytes = kBoxes * kTcTile * 128;      // [box][64 tokens][128 B]
-    static constexpr int kStageBytes = 2 * kKBytes;             // K then V
     static constexpr int kQOff = 0;
-    static constexpr int kStageOff = kQOff + 2 * kQBytes;
-    static constexpr int kBarOff = kStageOff + kTcStages * kStageBytes;
-    static constexpr int kRequest = kBarOff + 256;              // 17 mbarriers + tmem base word + flag
+    static constexpr int kKOff = kQOff + kQBytes;               // K ring
+    static constexpr int kVOff = kKOff + kTcRing * kKBytes;     // V ring
+    static constexpr int kBarOff = kVOff + kTcRing * kKBytes;
+    static constexpr int kRequest = kBarOff + 512;              // 43 mbarriers + tmem base word + flag
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------
@@ -179,6 +182,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     using L = TcSmem<D>;
+    constexpr int R = kTcRing;
     const AttnParams& p = dp.a;
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     const uint32_t base = smem_u32(tc_smem);
@@ -187,13 +191,14 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         if (tid == 0 && p.status) atomicExch(p.status, 10);
         return;
     }
-    const uint32_t sQ = base + L::kQOff, sStage = base + L::kStageOff;
+    const uint32_t sQ = base + L::kQOff, sK = base + L::kKOff, sV = base + L::kVOff;
     const uint32_t bars = base + L::kBarOff;
-    // barrier map (8 bytes each): full[5] empty[5] s_full[w][b] (4) p_ready[2] o_done[2] q_ready
-    const uint32_t bar_full = bars, bar_empty = bars + 40, bar_s = bars + 80, bar_p = bars + 112, bar_o = bars + 128,
-                   bar_q = bars + 144;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 160);
-    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 168);
+    // barrier map (8 bytes each): full_k[R] empty_k[R] full_v[R] empty_v[R] s_full[R] p_ready[R]
+    // o_done[R] q_ready
+    const uint32_t bar_full_k = bars, bar_empty_k = bars + 8 * R, bar_full_v = bars + 16 * R, bar_empty_v = bars + 24 * R,
+                   bar_s = bars + 32 * R, bar_p = bars + 40 * R, bar_o = bars + 48 * R, bar_q = bars + 56 * R;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 56 * R + 8);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 56 * R + 16);
 
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
     if (tid == 0) *poisoned = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
@@ -201,15 +206,15 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     if (*poisoned) return;
 
     const int item_lo = __ldg(dp.cta_begin + blockIdx.x), item_hi = __ldg(dp.cta_begin + blockIdx.x + 1);
+    if (item_lo >= item_hi) return;     // a CTA without work (uniform)
 
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
-        for (int i = 0; i < 2 * kTcStages; ++i) mbar_init(bar_full + 8 * i, 1);   // full[], empty[]
-        for (int i = 0; i < 4; ++i) mbar_init(bar_s + 8 * i, 1);       // s_full
-        for (int i = 0; i < 2; ++i) mbar_init(bar_p + 8 * i, 128);     // p_ready: every thread of a group
-        for (int i = 0; i < 2; ++i) mbar_init(bar_o + 8 * i, 1);       // o_done
-        mbar_init(bar_q, 256);                                         // q_ready: both groups
+        for (int i = 0; i < 5 * R; ++i) mbar_init(bar_full_k + 8 * i, 1);   // full/empty k/v, s_full
+        for (int i = 0; i < R; ++i) mbar_init(bar_p + 8 * i, 128);          // p_ready: every softmax thread
+        for (int i = 0; i < R; ++i) mbar_init(bar_o + 8 * i, 1);            // o_done
+        mbar_init(bar_q, 128);                                              // q_ready
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTcTmemCols);
@@ -217,35 +222,39 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o_col = R * kTcTile;    // O behind the S ring
     const int tiles_per_page = p.page_size >> 4;
 
-    if (warp == 8) {
-        // ---- TMA producer ----------------------------------------------------------------
+    if (warp == 4 || warp == 6) {
+        // ---- TMA producers: warp 4 streams K, warp 6 streams V ---------------------------------
+        const bool is_k = warp == 4;
+        const CUtensorMap* map = is_k ? &kmap : &vmap;
+        const uint32_t ring = is_k ? sK : sV;
+        const uint32_t full = is_k ? bar_full_k : bar_full_v;
+        const uint32_t empty = is_k ? bar_empty_k : bar_empty_v;
         bool ok = true;
-        int g = 0;
+        int t = 0;
         for (int item = item_lo; item < item_hi && ok; ++item) {
             const int32_t* it = p.items + static_cast<size_t>(item) * 8;
             const int page_off = __ldg(it + 2), kv_len = __ldg(it + 3), kvh = __ldg(it + 5);
             const int n_sub = (kv_len + 15) >> 4;
             const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
             const int32_t* item_pages = p.pages + page_off;
-            for (int j = 0; j < n_tiles; ++j, ++g) {
-                const int s = g % kTcStages;
-                if (g >= kTcStages) ok = mbar_wait(bar_empty + 8 * s, ((g / kTcStages) - 1) & 1);
+            for (int j = 0; j < n_tiles; ++j, ++t) {
+                const int s = t % R;
+                if (t >= R) ok = mbar_wait(empty + 8 * s, ((t / R) - 1) & 1);
                 if (!ok) break;
                 const int subs = min(4, n_sub - j * 4);
-                if (lane == 0) mbar_expect_tx(bar_full + 8 * s, subs * (2 * L::kBoxes * 2048));
+                if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
                 __syncwarp();
                 if (lane < subs) {
-                    const int t = j * 4 + lane;
-                    const int page = __ldg(item_pages + t / tiles_per_page);
-                    const int row0 = (t % tiles_per_page) << 4;
-                    const uint32_t dst = sStage + s * L::kStageBytes + lane * 2048;
+                    const int st = j * 4 + lane;
+                    const int page = __ldg(item_pages + st / tiles_per_page);
+                    const int row0 = (st % tiles_per_page) << 4;
 #pragma unroll
-                    for (int b = 0; b < L::kBoxes; ++b) {
-                        tma_load_4d(dst + b * (kTcTile * 128), &kmap, bar_full + 8 * s, b * 64, kvh, row0, page);
-                        tma_load_4d(dst + L::kKBytes + b * (kTcTile * 128), &vmap, bar_full + 8 * s, b * 64, kvh, row0, page);
-                    }
+                    for (int b = 0; b < L::kBoxes; ++b)
+                        tma_load_4d(ring + s * L::kKBytes + b * (kTcTile * 128) + lane * 2048, map, full + 8 * s,
+                                    b * 64, kvh, row0, page);
                 }
                 __syncwarp();
             }
@@ -254,101 +263,90 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         return;
     }
 
-    if (warp == 9) {
-        // ---- MMA issuer (one thread) ---------------------------------------------------------
+    if (warp == 5) {
+        // ---- MMA issuer (one thread) -------------------------------------------------------------
         if (lane != 0) return;
         const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
         const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
+        constexpr int kAhead = R - 1;           // S is computed this many tiles ahead of its P V
         bool ok = true;
-        int g = 0, g1 = 0, n_item = 0;
+        int g = 0, n_item = 0;
         for (int item = item_lo; item < item_hi; ++item, ++n_item) {
             const int32_t* it = p.items + static_cast<size_t>(item) * 8;
-            const int nq = __ldg(it + 1), kv_len = __ldg(it + 3);
-            const bool two = nq * p.hratio > 128;
+            const int kv_len = __ldg(it + 3);
             const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
             if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
             tc_fence_after();
 
-            const int nw = two ? 2 : 1;
-            auto wait_stage = [&](int j) {
-                const int s = (g + j) % kTcStages;
-                if (ok) ok = mbar_wait(bar_full + 8 * s, ((g + j) / kTcStages) & 1);
+            auto issue_qk = [&](int j) {                               // S(t) = Q K_j^T into ring slot t % R
+                const int t = g + j, s = t % R;
+                if (ok) ok = mbar_wait(bar_full_k + 8 * s, (t / R) & 1);
                 tc_fence_after();
-            };
-            auto issue_qk = [&](int w, int j) {                        // S_w = Q_w K_j^T into buffer (t & 1)
-                const int t = (w == 0 ? g : g1) + j;                   // this group's running tile index
-                const uint32_t k_addr = sStage + ((g + j) % kTcStages) * L::kStageBytes;
-                const uint32_t d_tmem = tmem_base + w * 128 + (t & 1) * kTcTile;
+                const uint32_t k_addr = sK + s * L::kKBytes;
+                if (!(p.debug & 4))
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t a = umma_desc_kmajor(sQ + w * L::kQBytes + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
+                    const uint64_t a = umma_desc_kmajor(sQ + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
                     const uint64_t b = umma_desc_kmajor(k_addr + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
-                    tc_mma(d_tmem, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                    tc_mma(tmem_base + s * kTcTile, a, b, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                tc_commit(bar_s + 8 * (2 * w + (t & 1)));
+                tc_commit(bar_s + 8 * s);
+                tc_commit(bar_empty_k + 8 * s);     // the K tile is free once this product has completed
             };
 
-            wait_stage(0);
-            for (int w = 0; w < nw; ++w) issue_qk(w, 0);
-            if (n_tiles > 1) {
-                wait_stage(1);
-                for (int w = 0; w < nw; ++w) issue_qk(w, 1);
-            }
+            for (int j = 0; j < min(kAhead, n_tiles); ++j) issue_qk(j);
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = (g + j) % kTcStages;
-                const uint32_t v_addr = sStage + s * L::kStageBytes + L::kKBytes;
-                for (int w = 0; w < nw; ++w) {
-                    const int t = (w == 0 ? g : g1) + j;
-                    if (ok) ok = mbar_wait(bar_p + 8 * w, t & 1);      // P_w(j) is in TMEM (over S_w(j))
-                    tc_fence_after();
-                    const uint32_t p_tmem = tmem_base + w * 128 + (t & 1) * kTcTile;
+                // slot (t + kAhead) % R held tile t - 1, whose P V was issued in the previous
+                // iteration; MMAs execute in issue order, so it may be overwritten now
+                if (j + kAhead < n_tiles) issue_qk(j + kAhead);
+                const int t = g + j, s = t % R;
+                if (ok) ok = mbar_wait(bar_full_v + 8 * s, (t / R) & 1);
+                if (ok) ok = mbar_wait(bar_p + 8 * s, (t / R) & 1);    // P(t) is in TMEM (over S(t))
+                tc_fence_after();
+                const uint32_t v_addr = sV + s * L::kKBytes;
+                if (!(p.debug & 8))
 #pragma unroll
-                    for (int ks = 0; ks < kTcTile / 16; ++ks) {
-                        const uint64_t b = umma_desc_mnmajor(v_addr + ks * 2048, kTcTile * 128);
-                        tc_mma_ts(tmem_base + 256 + w * 128, p_tmem + ks * 8, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    tc_commit(bar_o + 8 * w);
-                    // the S/P buffer of tile j is free again once the product above has read it
-                    // (MMAs execute in issue order): compute S two tiles ahead into it
-                    if (j + 2 < n_tiles) {
-                        if (w == 0) wait_stage(j + 2);
-                        issue_qk(w, j + 2);
-                    }
+                for (int ks = 0; ks < kTcTile / 16; ++ks) {
+                    const uint64_t b = umma_desc_mnmajor(v_addr + ks * 2048, kTcTile * 128);
+                    tc_mma_ts(tmem_base + tmem_o_col, tmem_base + s * kTcTile + ks * 8, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(bar_empty + 8 * s);                           // K/V stage free when everything above is done
+                tc_commit(bar_o + 8 * s);
+                tc_commit(bar_empty_v + 8 * s);
             }
             g += n_tiles;
-            if (two) g1 += n_tiles;
         }
         if (!ok && p.status) atomicExch(p.status, 13);
         return;
     }
 
-    // ---- softmax groups -----------------------------------------------------------------------
-    const int w = warp >> 2;                    // group 0 / 1
-    const int r = tid & 127;                    // row within the 128-row tile = TMEM lane
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t tmem_s = lane_addr + w * 128, tmem_o = lane_addr + 256 + w * 128;
+    // ---- softmax warps ---------------------------------------------------------------------------
+    const int r = tid;                          // row of the 128-row tile = TMEM lane
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t tmem_o = lane_addr + tmem_o_col;
     const float c = p.scale_log2;
     bool ok = true;
-    int t = 0;                                  // this group's running tile index
-    int g = 0;                                  // running tile index of the stage ring
-    int n_item = 0;
+    int t = 0;                                  // running tile index (all rings)
+    int o_seen = 0;                             // tiles whose P V is known to have completed
+    auto ensure_o = [&](int upto) {             // every o_done phase is consumed exactly once, in order
+        while (o_seen < upto) {
+            if (ok) ok = mbar_wait(bar_o + 8 * (o_seen % R), (o_seen / R) & 1);
+            ++o_seen;
+        }
+        tc_fence_after();
+    };
     for (int item = item_lo; item < item_hi; ++item) {
         const int32_t* it = p.items + static_cast<size_t>(item) * 8;
         const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kv_len = __ldg(it + 3), entry_base = __ldg(it + 4),
                   kvh = __ldg(it + 5);
         const int rows_valid = nq * p.hratio;
-        const bool active = (w == 0) || rows_valid > 128;
         const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
-        const int row = w * 128 + r;
 
         // Q rows of this item into the swizzled K-major layout (every MMA of the previous item has
-        // completed: its last o_done was awaited in the epilogue below)
-        if (active) {
+        // completed: its last o_done was consumed in the epilogue below)
+        {
             const uint4* src = nullptr;
-            if (row < rows_valid) {
-                const int qi = row / p.hratio, gg = row - qi * p.hratio;
+            if (r < rows_valid) {
+                const int qi = r / p.hratio, gg = r - qi * p.hratio;
                 const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
                              static_cast<int64_t>(kvh * p.hratio + gg) * p.q_head_stride;
                 src = reinterpret_cast<const uint4*>(q);
@@ -356,28 +354,26 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
 #pragma unroll
             for (int ch = 0; ch < D / 8; ++ch) {
                 const uint4 v = src ? __ldg(src + ch) : make_uint4(0, 0, 0, 0);
-                const uint32_t dst = sQ + w * L::kQBytes + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
+                const uint32_t dst = sQ + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
             }
             fence_async_smem();
         }
         tc_fence_before();
         mbar_arrive(bar_q);
-        if (!active) {
-            // an idle group must not run ahead: its next arrival may only count for the next phase
-            if (ok) ok = mbar_wait(bar_q, n_item & 1);
-            g += n_tiles;
-            ++n_item;
-            continue;
-        }
-        ++n_item;
 
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j, ++t) {
-            if (ok) ok = mbar_wait(bar_s + 8 * (2 * w + (t & 1)), (t >> 1) & 1);
+            const int s = t % R;
+            if (ok) ok = mbar_wait(bar_s + 8 * s, (t / R) & 1);
             tc_fence_after();
+            const uint32_t tmem_s = lane_addr + s * kTcTile;
             float sc[64];
-            tmem_ld64(tmem_s + (t & 1) * kTcTile, sc);
+            if (!(p.debug & 2)) tmem_ld64(tmem_s, sc);
+            else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) sc[i] = 0.f;
+            }
             const int valid = min(kTcTile, kv_len - j * kTcTile);
             if (valid < kTcTile) {
 #pragma unroll
@@ -392,13 +388,9 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             }
             const float mx = fmaxf(mx0, mx1);
 
-            bool o_waited = false;
             const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
             if (j > 0 && __any_sync(kFullMask, raise)) {
-                // O may only be touched once every earlier P V of this group has completed
-                if (ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
-                tc_fence_after();
-                o_waited = true;
+                ensure_o(t);            // O may only be touched once every earlier P V has completed
                 const float alpha = raise ? fast_exp2((m_used - mx) * c) : 1.f;
                 l *= alpha;
 #pragma unroll 1
@@ -414,50 +406,52 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const float off = m_used * c;
             float sum0 = 0.f, sum1 = 0.f;
             uint32_t packed[32];
+            if (!(p.debug & 1)) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
-                const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
-                sum0 += p0;
-                sum1 += p1;
-                packed[i] = Elt<T>::pack(p0, p1);
+                for (int i = 0; i < 32; ++i) {
+                    const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
+                    const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
+                    sum0 += p0;
+                    sum1 += p1;
+                    packed[i] = Elt<T>::pack(p0, p1);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) packed[i] = 0x3c003c00u + static_cast<uint32_t>(sc[i] > 1e30f);
+                sum0 = 64.f;
             }
             l += sum0 + sum1;
-            // P over the first 32 columns of the S buffer this thread has just read (its own lane)
-            tmem_st32(tmem_s + (t & 1) * kTcTile, packed);
-            if (valid < kTcTile && w == 0) {
+            // P over the first 32 columns of the S slot this thread has just read (its own lane)
+            if (!(p.debug & 16)) tmem_st32(tmem_s, packed);
+            if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
-                // zero them so that P = 0 times garbage cannot make a NaN.  The stage has landed
-                // (its S was computed from it) and both groups' P V products are issued after
-                // group 0 has arrived below.
-                const int s = (g + j) % kTcStages;
+                // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
+                if (ok) ok = mbar_wait(bar_full_v + 8 * s, (t / R) & 1);
                 const int rows = kTcTile - valid;
                 const int chunks = rows * 8 * L::kBoxes;
                 for (int i = r; i < chunks; i += 128) {
                     const int b = i / (rows * 8);
                     const int rem = i - b * rows * 8;
                     const int vrow = valid + (rem >> 3);
-                    const uint32_t dst = sStage + s * L::kStageBytes + L::kKBytes + b * (kTcTile * 128) + vrow * 128 + ((rem & 7) << 4);
+                    const uint32_t dst = sV + s * L::kKBytes + b * (kTcTile * 128) + vrow * 128 + ((rem & 7) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
                 }
                 fence_async_smem();
             }
-            // consume the o_done phase of the previous tile (issued a whole tile ago, so this does
-            // not stall); every phase is waited for exactly once, which keeps the parities in step
-            if (j > 0 && !o_waited && ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
+            // keep the o_done parities in step: the product of tile t - R was requested R - 1 tiles
+            // ago, so this does not stall
+            ensure_o(t - R + 1);
             tc_fence_before();
-            mbar_arrive(bar_p + 8 * w);
+            mbar_arrive(bar_p + 8 * s);
         }
-        g += n_tiles;
 
         // ---- item epilogue: O / l -> fp32 partial, LSE ---------------------------------------------
-        if (ok) ok = mbar_wait(bar_o + 8 * w, (t - 1) & 1);
-        tc_fence_after();
+        ensure_o(t);
         {
-            const bool store = ok && row < rows_valid;
+            const bool store = ok && r < rows_valid;
             size_t slot = 0;
-            if (row < rows_valid) {
-                const int qi = row / p.hratio, gg = row - qi * p.hratio;
+            if (r < rows_valid) {
+                const int qi = r / p.hratio, gg = r - qi * p.hratio;
                 slot = static_cast<size_t>(entry_base + qi) * p.hratio + gg;
             }
             const float inv = 1.f / l;
@@ -477,7 +471,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     tc_fence_before();
-    named_bar_sync(1, 256);
+    named_bar_sync(1, 128);
     if (warp == 0) tmem_dealloc(tmem_base, kTcTmemCols);
 }
 

@@ -240,80 +240,90 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                      [](const WorkItem& a, const WorkItem& b) { return a.cost > b.cost; });
 
     // ---- 6. dense items: equal token shares per persistent CTA ------------------
-    // Columns = (segment, <= dense_rows query rows); their token ranges are laid end to end
-    // and cut into `shares` equal parts.  Share s is executed by kv_heads CTAs, one per KV
-    // head (CTA id = s * kv_heads + head): the heads of a share walk the same pages at the
-    // same time, so every 2 KB cache row (all heads of a token) is fetched within a short
-    // window, as in the streaming kernel.
-    struct Column { const Segment* sg; int q0, nq; };
-    std::vector<Column> columns;
-    int64_t dense_total = 0;       // tokens over all columns (per KV head)
+    // The token ranges of the dense segments are laid end to end and cut into `shares` parts of
+    // equal cost.  A share is executed by kv_heads x row_lanes CTAs at the same time
+    // (CTA id = (share * kv_heads + head) * row_lanes + lane): one per KV head and per 128-row
+    // chunk of the queries (chunk c runs on lane c % row_lanes).  The CTAs of a share walk the
+    // same pages side by side, so a 2 KB cache row (all heads of a token) is fetched from HBM
+    // within a short window and the second row chunk finds it in L2.
+    struct DenseSeg { const Segment* sg; int chunks; };
+    std::vector<DenseSeg> dsegs;
+    int max_chunks = 1;
     for (const Segment& sg : segs) {
         if (!is_dense(sg)) continue;
-        const int nq = static_cast<int>(sg.queries.size());
-        for (int q0 = 0; q0 < nq; q0 += q_per_dense) {
-            columns.push_back(Column{&sg, q0, std::min(q_per_dense, nq - q0)});
-            dense_total += sg.tokens;
-        }
+        const int chunks = ceil_div(static_cast<int64_t>(sg.queries.size()), q_per_dense);
+        dsegs.push_back(DenseSeg{&sg, chunks});
+        max_chunks = std::max(max_chunks, chunks);
+        header_.dense_tokens += sg.tokens * chunks;
     }
-    header_.dense_tokens = dense_total;
+    const int row_lanes = std::min(2, max_chunks);
     std::vector<int32_t> cta_begin;
-    if (!columns.empty()) {
-        // cuts fall on multiples of `granule` tokens from the start of a column, so that every
+    if (!dsegs.empty()) {
+        // cuts fall on multiples of `granule` tokens from the start of a segment, so that every
         // piece starts on a page boundary and on a 64-token tile boundary
         int64_t granule = 64;
         while (granule % page_size != 0) granule += 64;
         const int64_t min_piece = std::max<int64_t>(granule, opt.dense_piece_tokens_min);
-        const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / kv_heads);
-        const int64_t shares = std::min<int64_t>(max_shares, std::max<int64_t>(1, dense_total / min_piece));
-        struct Piece { const Column* col; int64_t pos, take; };
+        auto passes = [&](const DenseSeg& d) { return static_cast<int64_t>(ceil_div(d.chunks, row_lanes)); };
+        int64_t total_cost = 0;
+        for (const DenseSeg& d : dsegs) total_cost += d.sg->tokens * passes(d);
+        const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / (static_cast<int64_t>(kv_heads) * row_lanes));
+        const int64_t shares = std::min<int64_t>(max_shares, std::max<int64_t>(1, total_cost / min_piece));
+        struct Piece { const DenseSeg* d; int64_t pos, take; };
         std::vector<std::vector<Piece>> share_pieces(1);
         int64_t used = 0, assigned = 0;
-        int64_t target = (dense_total + shares - 1) / shares;
-        target = (target + granule - 1) / granule * granule;
+        int64_t target = (total_cost + shares - 1) / shares;
         auto can_advance = [&]() { return static_cast<int64_t>(share_pieces.size()) < shares; };
         auto next_share = [&]() {
             share_pieces.emplace_back();
             used = 0;
             // re-balance: what is left, spread over the shares that are left
             const int64_t left = shares - static_cast<int64_t>(share_pieces.size()) + 1;
-            target = (dense_total - assigned + left - 1) / left;
-            target = (target + granule - 1) / granule * granule;
+            target = (total_cost - assigned + left - 1) / left;
         };
-        for (const Column& col : columns) {
+        for (size_t di = 0; di < dsegs.size(); ++di) {
+            const DenseSeg& d = dsegs[di];
+            const int64_t tokens = d.sg->tokens, w = passes(d);
             int64_t pos = 0;
-            const int64_t tokens = col.sg->tokens;
             while (pos < tokens) {
-                int64_t cap = target - used;
+                int64_t cap = (target - used + w - 1) / w;                  // tokens of this segment that still fit
                 if (!can_advance()) cap = tokens - pos;                     // the last share takes what is left
                 else if (cap < min_piece / 2 && used > 0) { next_share(); continue; }
                 int64_t take = std::min(tokens - pos, std::max(cap, granule));
-                if (take < tokens - pos) take = std::max<int64_t>(granule, take / granule * granule);
+                if (take < tokens - pos) take = std::max<int64_t>(granule, (take + granule - 1) / granule * granule);
+                take = std::min(take, tokens - pos);
                 // do not leave a sliver behind
                 if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
-                share_pieces.back().push_back(Piece{&col, pos, take});
-                used += take;
-                assigned += take;
+                share_pieces.back().push_back(Piece{&d, pos, take});
+                used += take * w;
+                assigned += take * w;
                 pos += take;
-                if (used >= target && can_advance() && (pos < tokens || &col != &columns.back())) next_share();
+                if (used >= target && can_advance() && (pos < tokens || di + 1 < dsegs.size())) next_share();
             }
         }
         for (const auto& pieces : share_pieces) {
             for (int h = 0; h < kv_heads; ++h) {
-                cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
-                for (const Piece& pc : pieces) {
-                    WorkItem it{};
-                    it.q_off = pc.col->sg->q_off + pc.col->q0;
-                    it.nq = pc.col->nq;
-                    it.page_off = pc.col->sg->page_off + static_cast<int32_t>(pc.pos / page_size);
-                    it.kv_len = static_cast<int32_t>(pc.take);
-                    it.entry_base = num_entries;
-                    it.kv_head = h;
-                    it.cost = static_cast<int32_t>(pc.take);
-                    num_entries += it.nq;
-                    for (int i = 0; i < it.nq; ++i)
-                        per_list[static_cast<size_t>(pc.col->sg->queries[pc.col->q0 + i]) * kv_heads + h] += 1;
-                    dense_items.push_back(it);
+                for (int lane = 0; lane < row_lanes; ++lane) {
+                    cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
+                    for (const Piece& pc : pieces) {
+                        const Segment* sg = pc.d->sg;
+                        const int nq_all = static_cast<int>(sg->queries.size());
+                        for (int chunk = lane; chunk < pc.d->chunks; chunk += row_lanes) {
+                            const int q0 = chunk * q_per_dense;
+                            WorkItem it{};
+                            it.q_off = sg->q_off + q0;
+                            it.nq = std::min(q_per_dense, nq_all - q0);
+                            it.page_off = sg->page_off + static_cast<int32_t>(pc.pos / page_size);
+                            it.kv_len = static_cast<int32_t>(pc.take);
+                            it.entry_base = num_entries;
+                            it.kv_head = h;
+                            it.cost = static_cast<int32_t>(pc.take);
+                            num_entries += it.nq;
+                            for (int i = 0; i < it.nq; ++i)
+                                per_list[static_cast<size_t>(sg->queries[q0 + i]) * kv_heads + h] += 1;
+                            dense_items.push_back(it);
+                        }
+                    }
                 }
             }
         }

@@ -43,7 +43,7 @@ struct PlanBucketView {
 struct WorkOptions {
     int num_sms = 148;
     int stream_rows = 16;              // query rows per streaming item
-    int dense_rows = 256;              // query rows per dense item (0 = dense kernel off)
+    int dense_rows = 128;              // query rows per dense item (0 = dense kernel off)
     int dense_min_rows = 17;           // segments with at least this many rows go to the dense kernel
     int chunk_tokens_min = 256;
     int chunk_tokens_max = 2048;

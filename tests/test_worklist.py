@@ -159,8 +159,9 @@ def test_full_configs_dedup_every_page(cfg, native_lib):
     load = np.array([dense[a:b, 3].sum() for a, b in ctas])
     assert load.sum() == header.dense_tokens * hk
     assert len(ctas) % hk == 0
-    assert load.max() <= 1.15 * load.mean() + 512, (load.max(), load.mean())
-    assert (dense[:, 1] * w.group <= 256).all()
+    busy = load[load > 0]
+    assert busy.max() <= 1.15 * busy.mean() + 1024, (busy.max(), busy.mean())
+    assert (dense[:, 1] * w.group <= 128).all()
     starts_on_tile = (dense[:, 2] - np.array([0])) >= 0
     assert starts_on_tile.all()
 
