@@ -19,8 +19,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libpat_b200.so")
 SOURCES = ["pat_tree.cpp", "pat_work.cpp", "pat_capi.cpp", "pat_decode.cu"]
-HEADERS = ["pat_tree.h", "pat_work.h", "pat_device.cuh", "pat_kernels.cuh",
-           os.path.join("..", "..", "include", "pat_b200.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))) + [
+    os.path.join("..", "..", "include", "pat_b200.h")]
 
 
 def _nvcc() -> str:

@@ -36,7 +36,8 @@ namespace pat {
 
 constexpr int kTcTile = 64;                 // tokens per tile
 constexpr int kTcRing = 6;                  // depth of the K, V and S rings
-constexpr int kTcThreads = 224;
+constexpr int kTcSoftmaxWarps = 8;
+constexpr int kTcThreads = (kTcSoftmaxWarps + 3) * 32;
 constexpr int kTcTmemCols = 512;
 constexpr float kTcLazyLog2 = 8.0f;
 
@@ -47,8 +48,9 @@ template <int D> struct TcSmem {
     static constexpr int kQOff = 0;
     static constexpr int kKOff = kQOff + kQBytes;               // K ring
     static constexpr int kVOff = kKOff + kTcRing * kKBytes;     // V ring
-    static constexpr int kBarOff = kVOff + kTcRing * kKBytes;
-    static constexpr int kRequest = kBarOff + 512;              // 43 mbarriers + tmem base word + flag
+    static constexpr int kBarOff = kVOff + kTcRing * kKBytes;   // 43 mbarriers + tmem base word + flag
+    static constexpr int kXchOff = kBarOff + 512;               // float[2][2][128]: row maxima / sums of the two column halves
+    static constexpr int kRequest = kXchOff + 2048;
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------
@@ -172,6 +174,46 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// 32 consecutive fp32 columns / 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// N consecutive fp32 columns (N = 32 or 64)
+template <int N> __device__ __forceinline__ void tmem_ld_f(uint32_t taddr, float (&v)[N]) {
+    if constexpr (N == 64) tmem_ld64(taddr, v); else tmem_ld32(taddr, v);
+}
+template <int N> __device__ __forceinline__ void tmem_st_f(uint32_t taddr, const float (&v)[N]) {
+    if constexpr (N == 64) tmem_st64(taddr, v);
+    else tmem_st32(taddr, reinterpret_cast<const uint32_t (&)[32]>(v));
+}
+
+__device__ __forceinline__ long long tc_clock() {
+    long long c;
+    asm volatile("mov.u64 %0, %clock64;" : "=l"(c));
+    return c;
+}
+
 struct DenseTcParams {
     AttnParams a;
     const int32_t* cta_begin;   // [num_ctas + 1] first dense item of each CTA
@@ -183,6 +225,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     using L = TcSmem<D>;
     constexpr int R = kTcRing;
+    constexpr int kSW = kTcSoftmaxWarps;        // warps 0..7 softmax, 8 = K producer, 9 = MMA, 10 = V producer
     const AttnParams& p = dp.a;
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     const uint32_t base = smem_u32(tc_smem);
@@ -199,6 +242,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                    bar_s = bars + 32 * R, bar_p = bars + 40 * R, bar_o = bars + 48 * R, bar_q = bars + 56 * R;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 56 * R + 8);
     volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 56 * R + 16);
+    float* xch = reinterpret_cast<float*>(tc_smem + L::kXchOff);      // [2][2][128]
 
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
     if (tid == 0) *poisoned = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
@@ -211,10 +255,10 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
         tma_prefetch_desc(&vmap);
-        for (int i = 0; i < 5 * R; ++i) mbar_init(bar_full_k + 8 * i, 1);   // full/empty k/v, s_full
-        for (int i = 0; i < R; ++i) mbar_init(bar_p + 8 * i, 128);          // p_ready: every softmax thread
-        for (int i = 0; i < R; ++i) mbar_init(bar_o + 8 * i, 1);            // o_done
-        mbar_init(bar_q, 128);                                              // q_ready
+        for (int i = 0; i < 5 * R; ++i) mbar_init(bar_full_k + 8 * i, 1);       // full/empty k/v, s_full
+        for (int i = 0; i < R; ++i) mbar_init(bar_p + 8 * i, kSW * 32);         // p_ready: every softmax thread
+        for (int i = 0; i < R; ++i) mbar_init(bar_o + 8 * i, 1);                // o_done
+        mbar_init(bar_q, kSW * 32);                                             // q_ready
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTcTmemCols);
@@ -224,10 +268,13 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o_col = R * kTcTile;    // O behind the S ring
     const int tiles_per_page = p.page_size >> 4;
+    // experiment: CTA 0 records clock64 time stamps of its first 96 tiles behind the status word
+    long long* trace = (p.debug & 64) && blockIdx.x == 0 && p.status ? reinterpret_cast<long long*>(p.status + 16) : nullptr;
+    auto stamp = [&](int tile, int what) { if (trace && tile < 96) trace[tile * 8 + what] = tc_clock(); };
 
-    if (warp == 4 || warp == 6) {
-        // ---- TMA producers: warp 4 streams K, warp 6 streams V ---------------------------------
-        const bool is_k = warp == 4;
+    if (warp == kSW || warp == kSW + 2) {
+        // ---- TMA producers: one warp streams K, one streams V ---------------------------------
+        const bool is_k = warp == kSW;
         const CUtensorMap* map = is_k ? &kmap : &vmap;
         const uint32_t ring = is_k ? sK : sV;
         const uint32_t full = is_k ? bar_full_k : bar_full_v;
@@ -263,12 +310,15 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         return;
     }
 
-    if (warp == 5) {
+    if (warp == kSW + 1) {
         // ---- MMA issuer (one thread) -------------------------------------------------------------
+        // Consecutive MMAs into the same accumulator tile are spaced by the accumulate latency, so
+        // three independent chains are interleaved: the second half of S(j + 4), the first half of
+        // S(j + 5) and O += P(j) V(j).
         if (lane != 0) return;
         const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
         const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
-        constexpr int kAhead = R - 1;           // S is computed this many tiles ahead of its P V
+        constexpr int kHalf = D / 32;           // k-steps in half of a QK product
         bool ok = true;
         int g = 0, n_item = 0;
         for (int item = item_lo; item < item_hi; ++item, ++n_item) {
@@ -278,40 +328,71 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
             tc_fence_after();
 
-            auto issue_qk = [&](int j) {                               // S(t) = Q K_j^T into ring slot t % R
+            auto wait_k = [&](int j) {
                 const int t = g + j, s = t % R;
                 if (ok) ok = mbar_wait(bar_full_k + 8 * s, (t / R) & 1);
                 tc_fence_after();
-                const uint32_t k_addr = sK + s * L::kKBytes;
-                if (!(p.debug & 4))
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t a = umma_desc_kmajor(sQ + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
-                    const uint64_t b = umma_desc_kmajor(k_addr + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
-                    tc_mma(tmem_base + s * kTcTile, a, b, idesc_qk, ks > 0 ? 1u : 0u);
-                }
+            };
+            auto qk_step = [&](int j, int ks) {                        // S(t) (+)= Q[:, 16 ks ..] K_j[:, 16 ks ..]^T
+                if (p.debug & 4) return;
+                const int s = (g + j) % R;
+                const uint64_t a = umma_desc_kmajor(sQ + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
+                const uint64_t b = umma_desc_kmajor(sK + s * L::kKBytes + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
+                tc_mma(tmem_base + s * kTcTile, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+            };
+            auto qk_done = [&](int j) {
+                const int s = (g + j) % R;
                 tc_commit(bar_s + 8 * s);
                 tc_commit(bar_empty_k + 8 * s);     // the K tile is free once this product has completed
+                stamp(g + j, 0);
+            };
+            auto pv_step = [&](int j, int ks) {                        // O (+)= P(t)[:, 16 ks ..] V_j[16 ks .., :]
+                if (p.debug & 8) return;
+                const int s = (g + j) % R;
+                const uint64_t b = umma_desc_mnmajor(sV + s * L::kKBytes + ks * 2048, kTcTile * 128);
+                tc_mma_ts(tmem_base + tmem_o_col, tmem_base + s * kTcTile + ks * 8, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
             };
 
-            for (int j = 0; j < min(kAhead, n_tiles); ++j) issue_qk(j);
+            // prologue: S(0..3) complete (two at a time), first half of S(4)
+            for (int j0 = 0; j0 < 4 && j0 < n_tiles; j0 += 2) {
+                const bool two = j0 + 1 < n_tiles;
+                wait_k(j0);
+                if (two) wait_k(j0 + 1);
+#pragma unroll
+                for (int ks = 0; ks < 2 * kHalf; ++ks) {
+                    qk_step(j0, ks);
+                    if (two) qk_step(j0 + 1, ks);
+                }
+                qk_done(j0);
+                if (two) qk_done(j0 + 1);
+            }
+            if (4 < n_tiles) {
+                wait_k(4);
+#pragma unroll
+                for (int ks = 0; ks < kHalf; ++ks) qk_step(4, ks);
+            }
             for (int j = 0; j < n_tiles; ++j) {
-                // slot (t + kAhead) % R held tile t - 1, whose P V was issued in the previous
-                // iteration; MMAs execute in issue order, so it may be overwritten now
-                if (j + kAhead < n_tiles) issue_qk(j + kAhead);
                 const int t = g + j, s = t % R;
+                const bool have_a = j + 4 < n_tiles, have_b = j + 5 < n_tiles;
+                if (have_b) wait_k(j + 5);
                 if (ok) ok = mbar_wait(bar_full_v + 8 * s, (t / R) & 1);
                 if (ok) ok = mbar_wait(bar_p + 8 * s, (t / R) & 1);    // P(t) is in TMEM (over S(t))
                 tc_fence_after();
-                const uint32_t v_addr = sV + s * L::kKBytes;
-                if (!(p.debug & 8))
+                stamp(t, 1);
+                // slot (t + 5) % R held tile t - 1, whose P V was issued in the previous iteration;
+                // MMAs execute in issue order, so it may be overwritten now
 #pragma unroll
-                for (int ks = 0; ks < kTcTile / 16; ++ks) {
-                    const uint64_t b = umma_desc_mnmajor(v_addr + ks * 2048, kTcTile * 128);
-                    tc_mma_ts(tmem_base + tmem_o_col, tmem_base + s * kTcTile + ks * 8, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                for (int i = 0; i < 4; ++i) {
+                    if (i < kHalf) {
+                        if (have_a) qk_step(j + 4, kHalf + i);
+                        if (have_b) qk_step(j + 5, i);
+                    }
+                    pv_step(j, i);
                 }
+                if (have_a) qk_done(j + 4);
                 tc_commit(bar_o + 8 * s);
                 tc_commit(bar_empty_v + 8 * s);
+                stamp(t, 2);
             }
             g += n_tiles;
         }
@@ -320,9 +401,14 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     }
 
     // ---- softmax warps ---------------------------------------------------------------------------
-    const int r = tid;                          // row of the 128-row tile = TMEM lane
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const uint32_t tmem_o = lane_addr + tmem_o_col;
+    // Thread (half, quad, lane) owns row r = 32 quad + lane (TMEM lane r) and the token columns
+    // [32 half, 32 half + 32) of every tile; the two threads of a row exchange their maxima through
+    // shared memory and keep identical copies of the running maximum.
+    constexpr int OC = D / 2;                   // O columns per thread
+    const int half = warp >> 2, quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t tmem_o = lane_addr + tmem_o_col + half * OC;
     const float c = p.scale_log2;
     bool ok = true;
     int t = 0;                                  // running tile index (all rings)
@@ -334,6 +420,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         }
         tc_fence_after();
     };
+    auto pair_sync = [&]() { named_bar_sync(2 + quad, 64); };   // the two warps that share TMEM lanes
     for (int item = item_lo; item < item_hi; ++item) {
         const int32_t* it = p.items + static_cast<size_t>(item) * 8;
         const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kv_len = __ldg(it + 3), entry_base = __ldg(it + 4),
@@ -341,8 +428,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const int rows_valid = nq * p.hratio;
         const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
 
-        // Q rows of this item into the swizzled K-major layout (every MMA of the previous item has
-        // completed: its last o_done was consumed in the epilogue below)
+        // Q rows of this item into the swizzled K-major layout, half a row per thread (every MMA of
+        // the previous item has completed: its last o_done was consumed in the epilogue below)
         {
             const uint4* src = nullptr;
             if (r < rows_valid) {
@@ -352,7 +439,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 src = reinterpret_cast<const uint4*>(q);
             }
 #pragma unroll
-            for (int ch = 0; ch < D / 8; ++ch) {
+            for (int i = 0; i < D / 16; ++i) {
+                const int ch = half * (D / 16) + i;
                 const uint4 v = src ? __ldg(src + ch) : make_uint4(0, 0, 0, 0);
                 const uint32_t dst = sQ + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
@@ -365,50 +453,51 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j, ++t) {
             const int s = t % R;
+            if (tid == 0) stamp(t, 3);
             if (ok) ok = mbar_wait(bar_s + 8 * s, (t / R) & 1);
             tc_fence_after();
-            const uint32_t tmem_s = lane_addr + s * kTcTile;
-            float sc[64];
-            if (!(p.debug & 2)) tmem_ld64(tmem_s, sc);
+            if (tid == 0) stamp(t, 4);
+            float sc[32];
+            if (!(p.debug & 2)) tmem_ld32(lane_addr + s * kTcTile + half * 32, sc);
             else {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) sc[i] = 0.f;
+                for (int i = 0; i < 32; ++i) sc[i] = 0.f;
             }
             const int valid = min(kTcTile, kv_len - j * kTcTile);
             if (valid < kTcTile) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (i >= valid) sc[i] = -INFINITY;
+                for (int i = 0; i < 32; ++i)
+                    if (half * 32 + i >= valid) sc[i] = -INFINITY;
             }
             float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
 #pragma unroll
-            for (int i = 4; i < 64; i += 4) {
+            for (int i = 4; i < 32; i += 4) {
                 mx0 = fmaxf(mx0, fmaxf(sc[i], sc[i + 1]));
                 mx1 = fmaxf(mx1, fmaxf(sc[i + 2], sc[i + 3]));
             }
-            const float mx = fmaxf(mx0, mx1);
+            float* xbuf = xch + (t & 1) * 256;
+            xbuf[half * 128 + r] = fmaxf(mx0, mx1);
+            pair_sync();
+            const float mx = fmaxf(fmaxf(mx0, mx1), xbuf[(half ^ 1) * 128 + r]);
 
             const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
             if (j > 0 && __any_sync(kFullMask, raise)) {
                 ensure_o(t);            // O may only be touched once every earlier P V has completed
                 const float alpha = raise ? fast_exp2((m_used - mx) * c) : 1.f;
                 l *= alpha;
-#pragma unroll 1
-                for (int h = 0; h < D / 64; ++h) {
-                    float ov[64];
-                    tmem_ld64(tmem_o + h * 64, ov);
+                float ov[OC];
+                tmem_ld_f<OC>(tmem_o, ov);
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) ov[i] *= alpha;
-                    tmem_st64(tmem_o + h * 64, ov);
-                }
+                for (int i = 0; i < OC; ++i) ov[i] *= alpha;
+                tmem_st_f<OC>(tmem_o, ov);
             }
             if (raise) m_used = mx;
             const float off = m_used * c;
             float sum0 = 0.f, sum1 = 0.f;
-            uint32_t packed[32];
+            uint32_t packed[16];
             if (!(p.debug & 1)) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
                     const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
                     sum0 += p0;
@@ -417,19 +506,19 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) packed[i] = 0x3c003c00u + static_cast<uint32_t>(sc[i] > 1e30f);
-                sum0 = 64.f;
+                for (int i = 0; i < 16; ++i) packed[i] = 0x3c003c00u + static_cast<uint32_t>(sc[i] > 1e30f);
+                sum0 = 32.f;
             }
             l += sum0 + sum1;
-            // P over the first 32 columns of the S slot this thread has just read (its own lane)
-            if (!(p.debug & 16)) tmem_st32(tmem_s, packed);
+            // P over the S columns this row has consumed: 16 packed columns per half
+            if (!(p.debug & 16)) tmem_st16(lane_addr + s * kTcTile + half * 16, packed);
             if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
                 if (ok) ok = mbar_wait(bar_full_v + 8 * s, (t / R) & 1);
                 const int rows = kTcTile - valid;
                 const int chunks = rows * 8 * L::kBoxes;
-                for (int i = r; i < chunks; i += 128) {
+                for (int i = tid; i < chunks; i += kSW * 32) {
                     const int b = i / (rows * 8);
                     const int rem = i - b * rows * 8;
                     const int vrow = valid + (rem >> 3);
@@ -443,35 +532,40 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             ensure_o(t - R + 1);
             tc_fence_before();
             mbar_arrive(bar_p + 8 * s);
+            if (tid == 0) stamp(t, 5);
         }
 
         // ---- item epilogue: O / l -> fp32 partial, LSE ---------------------------------------------
         ensure_o(t);
         {
+            // row sum = the two halves' sums (same buffer discipline as the maxima: parity of t)
+            float* xbuf = xch + (t & 1) * 256;
+            pair_sync();                        // partner has read the last tile's maximum
+            xbuf[half * 128 + r] = l;
+            pair_sync();
+            const float l_row = l + xbuf[(half ^ 1) * 128 + r];
+            pair_sync();                        // both have read before the buffer is reused
             const bool store = ok && r < rows_valid;
             size_t slot = 0;
             if (r < rows_valid) {
                 const int qi = r / p.hratio, gg = r - qi * p.hratio;
                 slot = static_cast<size_t>(entry_base + qi) * p.hratio + gg;
             }
-            const float inv = 1.f / l;
-#pragma unroll 1
-            for (int h = 0; h < D / 64; ++h) {
-                float ov[64];
-                tmem_ld64(tmem_o + h * 64, ov);
-                if (store) {
-                    float4* dst = reinterpret_cast<float4*>(p.part_o + slot * D + h * 64);
+            const float inv = 1.f / l_row;
+            float ov[OC];
+            tmem_ld_f<OC>(tmem_o, ov);
+            if (store) {
+                float4* dst = reinterpret_cast<float4*>(p.part_o + slot * D + half * OC);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
-                }
+                for (int i = 0; i < OC / 4; ++i)
+                    dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+                if (half == 0) p.part_lse[slot] = m_used * p.scale + logf(l_row);
             }
-            if (store) p.part_lse[slot] = m_used * p.scale + logf(l);
         }
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     tc_fence_before();
-    named_bar_sync(1, 128);
+    named_bar_sync(1, kSW * 32);
     if (warp == 0) tmem_dealloc(tmem_base, kTcTmemCols);
 }
 
