@@ -280,7 +280,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const uint32_t full = is_k ? bar_full_k : bar_full_v;
         const uint32_t empty = is_k ? bar_empty_k : bar_empty_v;
         bool ok = true;
-        int t = 0;
+        int t = 0, s = 0;
+        uint32_t ph = 1;                        // parity of the release that precedes the current use of slot s
         for (int item = item_lo; item < item_hi && ok; ++item) {
             const int32_t* it = p.items + static_cast<size_t>(item) * 8;
             const int page_off = __ldg(it + 2), kv_len = __ldg(it + 3), kvh = __ldg(it + 5);
@@ -288,8 +289,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
             const int32_t* item_pages = p.pages + page_off;
             for (int j = 0; j < n_tiles; ++j, ++t) {
-                const int s = t % R;
-                if (t >= R) ok = mbar_wait(empty + 8 * s, ((t / R) - 1) & 1);
+                if (t >= R) ok = mbar_wait(empty + 8 * s, ph);
                 if (!ok) break;
                 const int subs = min(4, n_sub - j * 4);
                 if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
@@ -304,6 +304,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                                     b * 64, kvh, row0, page);
                 }
                 __syncwarp();
+                if (++s == R) { s = 0; ph ^= 1; }
             }
         }
         if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
@@ -312,15 +313,27 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
 
     if (warp == kSW + 1) {
         // ---- MMA issuer (one thread) -------------------------------------------------------------
-        // Consecutive MMAs into the same accumulator tile are spaced by the accumulate latency, so
-        // three independent chains are interleaved: the second half of S(j + 4), the first half of
-        // S(j + 5) and O += P(j) V(j).
+        // The issuing thread is the narrowest resource of the CTA, so every descriptor is reduced
+        // to "base word + slot * stride + constant": the high words are constants, the low words
+        // are one integer add per MMA.  Per tile it interleaves the second half of S(t + 4), the
+        // first half of S(t + 5) and O += P(t) V(t).
         if (lane != 0) return;
         const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
         const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
-        constexpr int kHalf = D / 32;           // k-steps in half of a QK product
+        constexpr int kSteps = D / 16;          // k-steps of a QK product
+        constexpr int kHalf = kSteps / 2;
+        constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024 B, version 1, 128-B swizzle
+        constexpr uint32_t kSlotStep = static_cast<uint32_t>(L::kKBytes) >> 4;
+        const uint32_t q_lo = ((sQ >> 4) & 0x3fffu) | (1u << 16);            // K-major: leading offset unused (16 B)
+        const uint32_t k_lo0 = ((sK >> 4) & 0x3fffu) | (1u << 16);
+        const uint32_t v_lo0 = ((sV >> 4) & 0x3fffu) | (static_cast<uint32_t>((kTcTile * 128) >> 4) << 16);   // MN-major: next 64 elements
+        auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kHi) << 32) | lo; };
+        // offset (in 16-byte units) of k-step ks inside a K-major [rows x D] operand made of 64-element boxes
+        auto kstep_off = [](int ks, int rows) { return static_cast<uint32_t>(((ks >> 2) * rows * 128 + (ks & 3) * 32) >> 4); };
+        auto slot_add = [](int s, int d) { const int x = s + d; return x >= R ? x - R : x; };
+
         bool ok = true;
-        int g = 0, n_item = 0;
+        int t = 0, n_item = 0;                  // t: running tile index over all items
         for (int item = item_lo; item < item_hi; ++item, ++n_item) {
             const int32_t* it = p.items + static_cast<size_t>(item) * 8;
             const int kv_len = __ldg(it + 3);
@@ -328,73 +341,81 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
             tc_fence_after();
 
-            auto wait_k = [&](int j) {
-                const int t = g + j, s = t % R;
-                if (ok) ok = mbar_wait(bar_full_k + 8 * s, (t / R) & 1);
-                tc_fence_after();
-            };
-            auto qk_step = [&](int j, int ks) {                        // S(t) (+)= Q[:, 16 ks ..] K_j[:, 16 ks ..]^T
-                if (p.debug & 4) return;
-                const int s = (g + j) % R;
-                const uint64_t a = umma_desc_kmajor(sQ + (ks >> 2) * (128 * 128) + (ks & 3) * 32);
-                const uint64_t b = umma_desc_kmajor(sK + s * L::kKBytes + (ks >> 2) * (kTcTile * 128) + (ks & 3) * 32);
-                tc_mma(tmem_base + s * kTcTile, a, b, idesc_qk, ks > 0 ? 1u : 0u);
-            };
-            auto qk_done = [&](int j) {
-                const int s = (g + j) % R;
-                tc_commit(bar_s + 8 * s);
-                tc_commit(bar_empty_k + 8 * s);     // the K tile is free once this product has completed
-                stamp(g + j, 0);
-            };
-            auto pv_step = [&](int j, int ks) {                        // O (+)= P(t)[:, 16 ks ..] V_j[16 ks .., :]
-                if (p.debug & 8) return;
-                const int s = (g + j) % R;
-                const uint64_t b = umma_desc_mnmajor(sV + s * L::kKBytes + ks * 2048, kTcTile * 128);
-                tc_mma_ts(tmem_base + tmem_o_col, tmem_base + s * kTcTile + ks * 8, b, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-            };
-
             // prologue: S(0..3) complete (two at a time), first half of S(4)
-            for (int j0 = 0; j0 < 4 && j0 < n_tiles; j0 += 2) {
-                const bool two = j0 + 1 < n_tiles;
-                wait_k(j0);
-                if (two) wait_k(j0 + 1);
+            {
+                const int s0 = t % R;
+                const uint32_t ph0 = (t / R) & 1;
+                auto wait_k = [&](int d) {      // K tile of local tile d (d < R, so at most one wrap)
+                    const int s = slot_add(s0, d);
+                    if (ok) ok = mbar_wait(bar_full_k + 8 * s, s < s0 ? ph0 ^ 1 : ph0);
+                };
+                for (int j0 = 0; j0 < 4 && j0 < n_tiles; j0 += 2) {
+                    const bool two = j0 + 1 < n_tiles;
+                    const int sa = slot_add(s0, j0), sb = slot_add(s0, j0 + 1);
+                    wait_k(j0);
+                    if (two) wait_k(j0 + 1);
+                    tc_fence_after();
+                    if (!(p.debug & 4))
 #pragma unroll
-                for (int ks = 0; ks < 2 * kHalf; ++ks) {
-                    qk_step(j0, ks);
-                    if (two) qk_step(j0 + 1, ks);
+                    for (int ks = 0; ks < kSteps; ++ks) {
+                        tc_mma(tmem_base + sa * kTcTile, desc(q_lo + kstep_off(ks, 128)),
+                               desc(k_lo0 + sa * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
+                        if (two)
+                            tc_mma(tmem_base + sb * kTcTile, desc(q_lo + kstep_off(ks, 128)),
+                                   desc(k_lo0 + sb * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar_s + 8 * sa);
+                    tc_commit(bar_empty_k + 8 * sa);
+                    if (two) {
+                        tc_commit(bar_s + 8 * sb);
+                        tc_commit(bar_empty_k + 8 * sb);
+                    }
                 }
-                qk_done(j0);
-                if (two) qk_done(j0 + 1);
-            }
-            if (4 < n_tiles) {
-                wait_k(4);
+                if (4 < n_tiles) {
+                    const int sa = slot_add(s0, 4);
+                    wait_k(4);
+                    tc_fence_after();
+                    if (!(p.debug & 4))
 #pragma unroll
-                for (int ks = 0; ks < kHalf; ++ks) qk_step(4, ks);
+                    for (int ks = 0; ks < kHalf; ++ks)
+                        tc_mma(tmem_base + sa * kTcTile, desc(q_lo + kstep_off(ks, 128)),
+                               desc(k_lo0 + sa * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
+                }
             }
-            for (int j = 0; j < n_tiles; ++j) {
-                const int t = g + j, s = t % R;
+            int s = t % R;                      // slot and phase of the tile whose P V is issued next
+            uint32_t ph = (t / R) & 1;
+            for (int j = 0; j < n_tiles; ++j, ++t) {
                 const bool have_a = j + 4 < n_tiles, have_b = j + 5 < n_tiles;
-                if (have_b) wait_k(j + 5);
-                if (ok) ok = mbar_wait(bar_full_v + 8 * s, (t / R) & 1);
-                if (ok) ok = mbar_wait(bar_p + 8 * s, (t / R) & 1);    // P(t) is in TMEM (over S(t))
+                const int sa = slot_add(s, 4), sb = slot_add(s, 5);
+                stamp(t, 7);
+                if (have_b && ok) ok = mbar_wait(bar_full_k + 8 * sb, sb < s ? ph ^ 1 : ph);
+                if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
+                if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(t) is in TMEM (over S(t))
                 tc_fence_after();
                 stamp(t, 1);
-                // slot (t + 5) % R held tile t - 1, whose P V was issued in the previous iteration;
-                // MMAs execute in issue order, so it may be overwritten now
+                // slot sb held tile t - 1, whose P V was issued in the previous iteration; MMAs
+                // execute in issue order, so it may be overwritten now
+                const uint32_t ka = k_lo0 + sa * kSlotStep, kb = k_lo0 + sb * kSlotStep, vs = v_lo0 + s * kSlotStep;
+                const uint32_t ta = tmem_base + sa * kTcTile, tb = tmem_base + sb * kTcTile, tp = tmem_base + s * kTcTile;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    if (i < kHalf) {
-                        if (have_a) qk_step(j + 4, kHalf + i);
-                        if (have_b) qk_step(j + 5, i);
+                    if (i < kHalf && !(p.debug & 4)) {
+                        if (have_a) tc_mma(ta, desc(q_lo + kstep_off(kHalf + i, 128)), desc(ka + kstep_off(kHalf + i, kTcTile)), idesc_qk, 1u);
+                        if (have_b) tc_mma(tb, desc(q_lo + kstep_off(i, 128)), desc(kb + kstep_off(i, kTcTile)), idesc_qk, i > 0 ? 1u : 0u);
                     }
-                    pv_step(j, i);
+                    if (!(p.debug & 8))
+                        tc_mma_ts(tmem_base + tmem_o_col, tp + i * 8, desc(vs + i * (2048 >> 4)), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
                 }
-                if (have_a) qk_done(j + 4);
+                stamp(t, 6);
+                if (have_a) {
+                    tc_commit(bar_s + 8 * sa);
+                    tc_commit(bar_empty_k + 8 * sa);    // the K tile is free once this product has completed
+                }
                 tc_commit(bar_o + 8 * s);
                 tc_commit(bar_empty_v + 8 * s);
                 stamp(t, 2);
+                if (++s == R) { s = 0; ph ^= 1; }
             }
-            g += n_tiles;
         }
         if (!ok && p.status) atomicExch(p.status, 13);
         return;
@@ -412,11 +433,15 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     const float c = p.scale_log2;
     bool ok = true;
     int t = 0;                                  // running tile index (all rings)
-    int o_seen = 0;                             // tiles whose P V is known to have completed
+    int s = 0;                                  // t % R and the phase bit (t / R) & 1, kept incrementally
+    uint32_t ph = 0;
+    int o_seen = 0, o_slot = 0;                 // tiles whose P V is known to have completed
+    uint32_t o_ph = 0;
     auto ensure_o = [&](int upto) {             // every o_done phase is consumed exactly once, in order
         while (o_seen < upto) {
-            if (ok) ok = mbar_wait(bar_o + 8 * (o_seen % R), (o_seen / R) & 1);
+            if (ok) ok = mbar_wait(bar_o + 8 * o_slot, o_ph);
             ++o_seen;
+            if (++o_slot == R) { o_slot = 0; o_ph ^= 1; }
         }
         tc_fence_after();
     };
@@ -452,9 +477,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
 
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j, ++t) {
-            const int s = t % R;
             if (tid == 0) stamp(t, 3);
-            if (ok) ok = mbar_wait(bar_s + 8 * s, (t / R) & 1);
+            if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
             tc_fence_after();
             if (tid == 0) stamp(t, 4);
             float sc[32];
@@ -515,7 +539,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
-                if (ok) ok = mbar_wait(bar_full_v + 8 * s, (t / R) & 1);
+                if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
                 const int rows = kTcTile - valid;
                 const int chunks = rows * 8 * L::kBoxes;
                 for (int i = tid; i < chunks; i += kSW * 32) {
@@ -533,6 +557,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             tc_fence_before();
             mbar_arrive(bar_p + 8 * s);
             if (tid == 0) stamp(t, 5);
+            if (++s == R) { s = 0; ph ^= 1; }
         }
 
         // ---- item epilogue: O / l -> fp32 partial, LSE ---------------------------------------------
