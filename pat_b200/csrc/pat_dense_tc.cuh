@@ -7,23 +7,26 @@
 // reference's M=64 mma.sync tile (csrc/pat_fwd_kernel.h:25-299, csrc/kernel_traits.h:45-123)
 // for segments that many queries share.
 //
-//   warps 0-3: softmax.  Thread r owns query row r (= TMEM lane r).  Per 64-token tile it reads
-//            its row of S = Q K^T from TMEM (tcgen05.ld), does the online softmax without any
-//            cross-thread traffic and writes P (bf16/fp16 pairs) back into TMEM over the S
-//            columns it has just consumed (tcgen05.st); at the end of an item it reads O from
-//            TMEM and stores the normalised fp32 partial and its LSE.
-//   warp 4 / warp 6: TMA producers for K and for V, rings of 6 tiles of 64 tokens each (boxes of
-//            16 tokens x 64 elements, 128-byte swizzle - the layout the UMMA shared-memory
+//   warps 0-7: softmax.  Thread (half, quad, lane) owns query row r = 32 quad + lane (= TMEM lane
+//            r) and one half of the 128 token columns of every tile.  It reads its part of
+//            S = Q K^T from TMEM (tcgen05.ld), does the online softmax (the two threads of a row
+//            exchange their maxima through shared memory) and writes P (bf16/fp16 pairs) back
+//            into TMEM over the S columns the row has consumed (tcgen05.st); at the end of an
+//            item it reads its half of O from TMEM and stores the normalised fp32 partial.
+//   warp 8 / warp 10: TMA producers for K and for V, rings of 3 tiles of 128 tokens each (boxes
+//            of 16 tokens x 64 elements, 128-byte swizzle - the layout the UMMA shared-memory
 //            descriptors describe).  A K tile is released as soon as its S = Q K^T has
 //            completed, a V tile when its P V has.
-//   warp 5:  one thread issues every MMA: S(j) = Q K_j^T (M128 N64 K16 x D/16, both operands
-//            from shared memory) five tiles ahead of the softmax, and O += P(j) V_j (M128 N=D
-//            K16 x 4, A = P from TMEM, B = V from shared memory); completion is signalled with
+//   warp 9:  one thread issues every MMA: S(t) = Q K_t^T (M128 N128 K16 x D/16, both operands
+//            from shared memory) two tiles ahead of the softmax, and O += P(t) V_t (M128 N=D
+//            K16 x 8, A = P from TMEM, B = V from shared memory); completion is signalled with
 //            tcgen05.commit on mbarriers.
 //
-// Why so deep: a tcgen05.commit needs of the order of a microsecond to reach its mbarrier, about
-// three times the softmax time of a tile, so S is kept in a ring of six TMEM buffers (6 x 64
-// columns + D columns of O) and no thread ever waits for a product it has just requested.
+// Two measured facts shape the pipeline.  A tcgen05.commit needs of the order of a microsecond
+// to reach its mbarrier, so S lives in a ring of three 128-column TMEM buffers (3 x 128 + D
+// columns of O = 512) and no thread waits for a product it has just requested.  And one thread
+// issues an MMA only about every 80 clocks whatever its size, so the products are made as large
+// as TMEM allows (N = 128 tokens for Q K^T).
 // The running maximum is only raised when a tile exceeds it by more than 2^8 (the offset
 // cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
 // Every mbarrier wait is bounded; a wait that gives up records a code in the status word,
@@ -34,8 +37,8 @@
 
 namespace pat {
 
-constexpr int kTcTile = 64;                 // tokens per tile
-constexpr int kTcRing = 6;                  // depth of the K, V and S rings
+constexpr int kTcTile = 128;                // tokens per tile
+constexpr int kTcRing = 3;                  // depth of the K, V and S rings
 constexpr int kTcSoftmaxWarps = 8;
 constexpr int kTcThreads = (kTcSoftmaxWarps + 3) * 32;
 constexpr int kTcTmemCols = 512;
@@ -44,7 +47,7 @@ constexpr float kTcLazyLog2 = 8.0f;
 template <int D> struct TcSmem {
     static constexpr int kBoxes = D / 64;
     static constexpr int kQBytes = kBoxes * 128 * 128;          // [box][128 rows][128 B]
-    static constexpr int kKBytes = kBoxes * kTcTile * 128;      // [box][64 tokens][128 B]
+    static constexpr int kKBytes = kBoxes * kTcTile * 128;      // [box][128 tokens][128 B]
     static constexpr int kQOff = 0;
     static constexpr int kKOff = kQOff + kQBytes;               // K ring
     static constexpr int kVOff = kKOff + kTcRing * kKBytes;     // V ring
@@ -291,11 +294,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             for (int j = 0; j < n_tiles; ++j, ++t) {
                 if (t >= R) ok = mbar_wait(empty + 8 * s, ph);
                 if (!ok) break;
-                const int subs = min(4, n_sub - j * 4);
+                constexpr int kSub = kTcTile / 16;
+                const int subs = min(kSub, n_sub - j * kSub);
                 if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
                 __syncwarp();
                 if (lane < subs) {
-                    const int st = j * 4 + lane;
+                    const int st = j * kSub + lane;
                     const int page = __ldg(item_pages + st / tiles_per_page);
                     const int row0 = (st % tiles_per_page) << 4;
 #pragma unroll
@@ -315,13 +319,11 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         // ---- MMA issuer (one thread) -------------------------------------------------------------
         // The issuing thread is the narrowest resource of the CTA, so every descriptor is reduced
         // to "base word + slot * stride + constant": the high words are constants, the low words
-        // are one integer add per MMA.  Per tile it interleaves the second half of S(t + 4), the
-        // first half of S(t + 5) and O += P(t) V(t).
+        // are one integer add per MMA.  Per tile it interleaves S(t + 2) with O += P(t) V(t).
         if (lane != 0) return;
         const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
         const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
         constexpr int kSteps = D / 16;          // k-steps of a QK product
-        constexpr int kHalf = kSteps / 2;
         constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024 B, version 1, 128-B swizzle
         constexpr uint32_t kSlotStep = static_cast<uint32_t>(L::kKBytes) >> 4;
         const uint32_t q_lo = ((sQ >> 4) & 0x3fffu) | (1u << 16);            // K-major: leading offset unused (16 B)
@@ -341,68 +343,48 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
             tc_fence_after();
 
-            // prologue: S(0..3) complete (two at a time), first half of S(4)
-            {
-                const int s0 = t % R;
-                const uint32_t ph0 = (t / R) & 1;
-                auto wait_k = [&](int d) {      // K tile of local tile d (d < R, so at most one wrap)
-                    const int s = slot_add(s0, d);
-                    if (ok) ok = mbar_wait(bar_full_k + 8 * s, s < s0 ? ph0 ^ 1 : ph0);
-                };
-                for (int j0 = 0; j0 < 4 && j0 < n_tiles; j0 += 2) {
-                    const bool two = j0 + 1 < n_tiles;
-                    const int sa = slot_add(s0, j0), sb = slot_add(s0, j0 + 1);
-                    wait_k(j0);
-                    if (two) wait_k(j0 + 1);
-                    tc_fence_after();
-                    if (!(p.debug & 4))
-#pragma unroll
-                    for (int ks = 0; ks < kSteps; ++ks) {
-                        tc_mma(tmem_base + sa * kTcTile, desc(q_lo + kstep_off(ks, 128)),
-                               desc(k_lo0 + sa * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
-                        if (two)
-                            tc_mma(tmem_base + sb * kTcTile, desc(q_lo + kstep_off(ks, 128)),
-                                   desc(k_lo0 + sb * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
-                    }
-                    tc_commit(bar_s + 8 * sa);
-                    tc_commit(bar_empty_k + 8 * sa);
-                    if (two) {
-                        tc_commit(bar_s + 8 * sb);
-                        tc_commit(bar_empty_k + 8 * sb);
-                    }
-                }
-                if (4 < n_tiles) {
-                    const int sa = slot_add(s0, 4);
-                    wait_k(4);
-                    tc_fence_after();
-                    if (!(p.debug & 4))
-#pragma unroll
-                    for (int ks = 0; ks < kHalf; ++ks)
-                        tc_mma(tmem_base + sa * kTcTile, desc(q_lo + kstep_off(ks, 128)),
-                               desc(k_lo0 + sa * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
-                }
-            }
             int s = t % R;                      // slot and phase of the tile whose P V is issued next
             uint32_t ph = (t / R) & 1;
+            // prologue: S(0) and S(1)
+            {
+                const bool two = n_tiles > 1;
+                const int s1 = slot_add(s, 1);
+                if (ok) ok = mbar_wait(bar_full_k + 8 * s, ph);
+                if (two && ok) ok = mbar_wait(bar_full_k + 8 * s1, s1 < s ? ph ^ 1 : ph);
+                tc_fence_after();
+                if (!(p.debug & 4))
+#pragma unroll
+                for (int ks = 0; ks < kSteps; ++ks) {
+                    tc_mma(tmem_base + s * kTcTile, desc(q_lo + kstep_off(ks, 128)),
+                           desc(k_lo0 + s * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
+                    if (two)
+                        tc_mma(tmem_base + s1 * kTcTile, desc(q_lo + kstep_off(ks, 128)),
+                               desc(k_lo0 + s1 * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_s + 8 * s);
+                tc_commit(bar_empty_k + 8 * s);
+                if (two) {
+                    tc_commit(bar_s + 8 * s1);
+                    tc_commit(bar_empty_k + 8 * s1);
+                }
+            }
             for (int j = 0; j < n_tiles; ++j, ++t) {
-                const bool have_a = j + 4 < n_tiles, have_b = j + 5 < n_tiles;
-                const int sa = slot_add(s, 4), sb = slot_add(s, 5);
+                const bool have_a = j + 2 < n_tiles;
+                const int sa = slot_add(s, 2);
                 stamp(t, 7);
-                if (have_b && ok) ok = mbar_wait(bar_full_k + 8 * sb, sb < s ? ph ^ 1 : ph);
+                if (have_a && ok) ok = mbar_wait(bar_full_k + 8 * sa, sa < s ? ph ^ 1 : ph);
                 if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
                 if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(t) is in TMEM (over S(t))
                 tc_fence_after();
                 stamp(t, 1);
-                // slot sb held tile t - 1, whose P V was issued in the previous iteration; MMAs
-                // execute in issue order, so it may be overwritten now
-                const uint32_t ka = k_lo0 + sa * kSlotStep, kb = k_lo0 + sb * kSlotStep, vs = v_lo0 + s * kSlotStep;
-                const uint32_t ta = tmem_base + sa * kTcTile, tb = tmem_base + sb * kTcTile, tp = tmem_base + s * kTcTile;
+                // slot sa held tile t - 1, whose P V was issued in the previous iteration; MMAs
+                // execute in issue order, so S(t + 2) may overwrite it now
+                const uint32_t ka = k_lo0 + sa * kSlotStep, vs = v_lo0 + s * kSlotStep;
+                const uint32_t ta = tmem_base + sa * kTcTile, tp = tmem_base + s * kTcTile;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (i < kHalf && !(p.debug & 4)) {
-                        if (have_a) tc_mma(ta, desc(q_lo + kstep_off(kHalf + i, 128)), desc(ka + kstep_off(kHalf + i, kTcTile)), idesc_qk, 1u);
-                        if (have_b) tc_mma(tb, desc(q_lo + kstep_off(i, 128)), desc(kb + kstep_off(i, kTcTile)), idesc_qk, i > 0 ? 1u : 0u);
-                    }
+                for (int i = 0; i < kTcTile / 16; ++i) {
+                    if (i < kSteps && have_a && !(p.debug & 4))
+                        tc_mma(ta, desc(q_lo + kstep_off(i, 128)), desc(ka + kstep_off(i, kTcTile)), idesc_qk, i > 0 ? 1u : 0u);
                     if (!(p.debug & 8))
                         tc_mma_ts(tmem_base + tmem_o_col, tp + i * 8, desc(vs + i * (2048 >> 4)), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
                 }
@@ -481,21 +463,22 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
             tc_fence_after();
             if (tid == 0) stamp(t, 4);
-            float sc[32];
-            if (!(p.debug & 2)) tmem_ld32(lane_addr + s * kTcTile + half * 32, sc);
+            constexpr int CH = kTcTile / 2;     // token columns per thread
+            float sc[CH];
+            if (!(p.debug & 2)) tmem_ld_f<CH>(lane_addr + s * kTcTile + half * CH, sc);
             else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sc[i] = 0.f;
+                for (int i = 0; i < CH; ++i) sc[i] = 0.f;
             }
             const int valid = min(kTcTile, kv_len - j * kTcTile);
             if (valid < kTcTile) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (half * 32 + i >= valid) sc[i] = -INFINITY;
+                for (int i = 0; i < CH; ++i)
+                    if (half * CH + i >= valid) sc[i] = -INFINITY;
             }
             float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
 #pragma unroll
-            for (int i = 4; i < 32; i += 4) {
+            for (int i = 4; i < CH; i += 4) {
                 mx0 = fmaxf(mx0, fmaxf(sc[i], sc[i + 1]));
                 mx1 = fmaxf(mx1, fmaxf(sc[i + 2], sc[i + 3]));
             }
@@ -518,10 +501,10 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (raise) m_used = mx;
             const float off = m_used * c;
             float sum0 = 0.f, sum1 = 0.f;
-            uint32_t packed[16];
+            uint32_t packed[CH / 2];
             if (!(p.debug & 1)) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < CH / 2; ++i) {
                     const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
                     const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
                     sum0 += p0;
@@ -530,12 +513,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) packed[i] = 0x3c003c00u + static_cast<uint32_t>(sc[i] > 1e30f);
-                sum0 = 32.f;
+                for (int i = 0; i < CH / 2; ++i) packed[i] = 0x3c003c00u + static_cast<uint32_t>(sc[i] > 1e30f);
+                sum0 = static_cast<float>(CH);
             }
             l += sum0 + sum1;
-            // P over the S columns this row has consumed: 16 packed columns per half
-            if (!(p.debug & 16)) tmem_st16(lane_addr + s * kTcTile + half * 16, packed);
+            // P over the S columns this row has consumed: CH / 2 packed columns per half
+            if (!(p.debug & 16)) tmem_st32(lane_addr + s * kTcTile + half * (CH / 2), packed);
             if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
