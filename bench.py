@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA graph replays")
+    ap.add_argument("--flags", type=int, default=0, help="extra launch flags (include/pat_b200.h), e.g. 16 = no overlap")
     ap.add_argument("--scale-down", type=int, default=1,
                     help="divide every segment length by this factor (profiling captures on a small case)")
     return ap.parse_args()
@@ -244,7 +245,7 @@ def main():
         flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
     def step(flags=0):
-        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags)
+        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags | args.flags)
 
     def barrier():
         torch.cuda.synchronize()

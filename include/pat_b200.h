@@ -122,7 +122,9 @@ typedef struct pat_work_options {
     int32_t dense_piece_tokens_min; /* a dense CTA share is not cut below about this; 0 = default */
     int32_t items_per_sm;        /* 0 = default */
     int32_t disable_dense;       /* 1 = every segment goes through the streaming kernel */
-    int32_t reserved;
+    int32_t dense_tile_ns;       /* estimated time of one 128-token dense tile; sizes the dense kernel's share
+                                    of the SMs when it runs beside the streaming kernel.  0 = default,
+                                    < 0 = the dense kernel gets every SM */
 } pat_work_options;
 
 typedef struct pat_work_header {
@@ -160,7 +162,9 @@ const int32_t* pat_work_blob(const pat_work* w, size_t* words);
  * ------------------------------------------------------------------------- */
 enum { PAT_DTYPE_FP16 = 0, PAT_DTYPE_BF16 = 1 };
 enum { PAT_SKIP_STREAM = 1, PAT_SKIP_DENSE = 2, PAT_SKIP_MERGE = 4,
-       PAT_DENSE_MMA_SYNC = 8 /* run the dense tiles on the legacy mma.sync kernel instead of tcgen05 */ };
+       PAT_DENSE_MMA_SYNC = 8, /* run the dense tiles on the legacy mma.sync kernel instead of tcgen05 */
+       PAT_NO_OVERLAP = 16     /* launch the dense kernel after the streaming kernel on the caller's stream,
+                                  not beside it on an internal stream */ };
 
 typedef struct pat_decode_args {
     /* tensors (device pointers), strides in elements, last dimension contiguous */

@@ -32,7 +32,7 @@ class PlanBucket(C.Structure):
 class WorkOptions(C.Structure):
     _fields_ = [("num_sms", C.c_int32), ("dense_min_rows", C.c_int32), ("chunk_tokens_min", C.c_int32),
                 ("chunk_tokens_max", C.c_int32), ("dense_piece_tokens_min", C.c_int32),
-                ("items_per_sm", C.c_int32), ("disable_dense", C.c_int32), ("reserved", C.c_int32)]
+                ("items_per_sm", C.c_int32), ("disable_dense", C.c_int32), ("dense_tile_ns", C.c_int32)]
 
 
 class WorkHeader(C.Structure):

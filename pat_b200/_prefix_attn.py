@@ -26,7 +26,7 @@ class WorkConfig:
     """Tuning knobs of the work-list builder (0 = library default)."""
 
     __slots__ = ("num_sms", "dense_min_rows", "chunk_tokens_min", "chunk_tokens_max",
-                 "dense_piece_tokens_min", "items_per_sm", "disable_dense")
+                 "dense_piece_tokens_min", "items_per_sm", "disable_dense", "dense_tile_ns")
 
     def __init__(self, **kw):
         for name in self.__slots__:

@@ -32,6 +32,7 @@ pat::WorkOptions to_options(const pat_work_options* o) {
     if (o->chunk_tokens_max > 0) w.chunk_tokens_max = o->chunk_tokens_max;
     if (o->dense_piece_tokens_min > 0) w.dense_piece_tokens_min = o->dense_piece_tokens_min;
     if (o->items_per_sm > 0) w.items_per_sm = o->items_per_sm;
+    if (o->dense_tile_ns != 0) w.dense_tile_ns = o->dense_tile_ns;
     if (o->disable_dense) { w.dense_rows = 0; w.dense_min_rows = 1 << 30; }
     return w;
 }

@@ -59,6 +59,40 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 thread_local int g_last_launches = 0;
 constexpr int kMaxDevices = 64;
 
+// A second stream per (host thread, device) on which the dense kernel runs beside the streaming
+// kernel, with the two events that fork it from and join it to the caller's stream.  Created on
+// the first call that needs them; the event pattern is the one stream capture understands.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    ~SideStream() {
+        if (join) cudaEventDestroy(join);
+        if (fork) cudaEventDestroy(fork);
+        if (stream) cudaStreamDestroy(stream);
+    }
+};
+thread_local SideStream g_side[kMaxDevices];
+
+SideStream* side_stream(int dev) {
+    SideStream& s = g_side[dev];
+    if (s.stream) return &s;
+    int least = 0, greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
+    cudaStream_t st = nullptr;
+    cudaEvent_t f = nullptr, j = nullptr;
+    if (cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, greatest) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&f, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&j, cudaEventDisableTiming) != cudaSuccess) {
+        if (f) cudaEventDestroy(f);
+        cudaStreamDestroy(st);
+        return nullptr;
+    }
+    s.stream = st;
+    s.fork = f;
+    s.join = j;
+    return &s;
+}
+
 template <typename T, int D>
 int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     using namespace pat;
@@ -92,7 +126,42 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     p.debug = a.flags >> 8;
 
     int launches = 0;
-    if (a.work.num_stream_items > 0 && !(a.flags & PAT_SKIP_STREAM)) {
+    const bool streaming = a.work.num_stream_items > 0 && !(a.flags & PAT_SKIP_STREAM);
+    const bool dense = a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE);
+    const bool dense_tc = dense && !(a.flags & PAT_DENSE_MMA_SYNC);
+
+    // The streaming kernel is bound by HBM, the dense kernel by the tensor and special-function
+    // units of the SMs it holds and it needs few of them when the work list sized it so
+    // (num_dense_ctas below the SM count).  So the dense kernel goes first, on a side stream, and
+    // the streaming kernel fills the SMs it leaves - and takes them over as its CTAs retire.
+    SideStream* side = nullptr;
+    if (streaming && dense_tc && !(a.flags & PAT_NO_OVERLAP)) {
+        side = side_stream(dev);
+        if (!side) return PAT_ERR_CUDA;
+        if (cudaEventRecord(side->fork, stream) != cudaSuccess ||
+            cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
+            return PAT_ERR_CUDA;
+    }
+    if (dense_tc) {
+        // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
+        static bool configured[kMaxDevices] = {};
+        auto kern = dense_tc_kernel<T, D>;
+        constexpr int smem = TcSmem<D>::kRequest;
+        if (!configured[dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return PAT_ERR_CUDA;
+            configured[dev] = true;
+        }
+        AttnParams pd = p;
+        pd.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
+        pd.num_items = a.work.num_dense_items;
+        DenseTcParams dp{};
+        dp.a = pd;
+        dp.cta_begin = a.work_blob + a.work.dense_cta_off;
+        kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, side ? side->stream : stream>>>(dp, kmap, vmap);
+        ++launches;
+    }
+    if (streaming) {
         static bool configured[kMaxDevices] = {};
         auto kern = stream_kernel<T, D>;
         constexpr int smem = stream_smem_bytes<D>();
@@ -108,25 +177,12 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         kern<<<static_cast<unsigned>(grid), kStreamWarps * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
-    const bool dense = a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE);
-    p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
-    p.num_items = a.work.num_dense_items;
-    if (dense && !(a.flags & PAT_DENSE_MMA_SYNC)) {
-        // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
-        static bool configured[kMaxDevices] = {};
-        auto kern = dense_tc_kernel<T, D>;
-        constexpr int smem = TcSmem<D>::kRequest;
-        if (!configured[dev]) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                return PAT_ERR_CUDA;
-            configured[dev] = true;
-        }
-        DenseTcParams dp{};
-        dp.a = p;
-        dp.cta_begin = a.work_blob + a.work.dense_cta_off;
-        kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, stream>>>(dp, kmap, vmap);
-        ++launches;
-    } else if (dense) {
+    if (side) {
+        if (cudaEventRecord(side->join, side->stream) != cudaSuccess ||
+            cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess)
+            return PAT_ERR_CUDA;
+    }
+    if (dense && !dense_tc) {
         // the same items on the legacy mma.sync path (kept for comparison): one CTA per
         // (item, 128-row half)
         static bool configured[kMaxDevices] = {};
@@ -137,6 +193,8 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
                 return PAT_ERR_CUDA;
             configured[dev] = true;
         }
+        p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
+        p.num_items = a.work.num_dense_items;
         kern<<<dim3(static_cast<unsigned>(a.work.num_dense_items), 2), (kDenseWarps + 1) * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
@@ -257,5 +315,6 @@ extern "C" int pat_b200_decode_static_scratch(const pat_decode_args* args, void*
     pat_decode_args local = *args;
     local.workspace = ptr;
     local.workspace_bytes = PAT_B200_STATIC_SCRATCH_BYTES;
+    local.flags |= PAT_NO_OVERLAP;      // no side stream: this entry point creates nothing
     return pat_b200_decode(&local, stream_handle);
 }

@@ -68,6 +68,12 @@ __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -254,6 +260,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
 
     const int item_lo = __ldg(dp.cta_begin + blockIdx.x), item_hi = __ldg(dp.cta_begin + blockIdx.x + 1);
     if (item_lo >= item_hi) return;     // a CTA without work (uniform)
+    if ((p.debug & 128) && (blockIdx.x & 1)) return;    // experiment: odd CTAs idle
 
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
@@ -273,7 +280,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     const int tiles_per_page = p.page_size >> 4;
     // experiment: CTA 0 records clock64 time stamps of its first 96 tiles behind the status word
     long long* trace = (p.debug & 64) && blockIdx.x == 0 && p.status ? reinterpret_cast<long long*>(p.status + 16) : nullptr;
-    auto stamp = [&](int tile, int what) { if (trace && tile < 96) trace[tile * 8 + what] = tc_clock(); };
+    auto stamp = [&](int tile, int what) { if (trace && tile < 96) trace[tile * 16 + what] = tc_clock(); };
 
     if (warp == kSW || warp == kSW + 2) {
         // ---- TMA producers: one warp streams K, one streams V ---------------------------------
@@ -294,6 +301,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             for (int j = 0; j < n_tiles; ++j, ++t) {
                 if (t >= R) ok = mbar_wait(empty + 8 * s, ph);
                 if (!ok) break;
+                if (is_k && lane == 0) stamp(t, 0);
                 constexpr int kSub = kTcTile / 16;
                 const int subs = min(kSub, n_sub - j * kSub);
                 if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
@@ -320,18 +328,18 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         // The issuing thread is the narrowest resource of the CTA, so every descriptor is reduced
         // to "base word + slot * stride + constant": the high words are constants, the low words
         // are one integer add per MMA.  Per tile it interleaves S(t + 2) with O += P(t) V(t).
-        if (lane != 0) return;
+        // The whole warp runs the loop (warp-uniform control flow and operands, which the compiler can
+        // keep in uniform registers); one elected lane issues the tcgen05 instructions.
         const uint32_t idesc_qk = umma_idesc<T>(128, kTcTile, false);
         const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
         constexpr int kSteps = D / 16;          // k-steps of a QK product
+        static_assert(kTcTile == 128, "the k-step arithmetic below assumes K tiles of 128 rows, like Q");
         constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024 B, version 1, 128-B swizzle
         constexpr uint32_t kSlotStep = static_cast<uint32_t>(L::kKBytes) >> 4;
         const uint32_t q_lo = ((sQ >> 4) & 0x3fffu) | (1u << 16);            // K-major: leading offset unused (16 B)
         const uint32_t k_lo0 = ((sK >> 4) & 0x3fffu) | (1u << 16);
         const uint32_t v_lo0 = ((sV >> 4) & 0x3fffu) | (static_cast<uint32_t>((kTcTile * 128) >> 4) << 16);   // MN-major: next 64 elements
         auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kHi) << 32) | lo; };
-        // offset (in 16-byte units) of k-step ks inside a K-major [rows x D] operand made of 64-element boxes
-        auto kstep_off = [](int ks, int rows) { return static_cast<uint32_t>(((ks >> 2) * rows * 128 + (ks & 3) * 32) >> 4); };
         auto slot_add = [](int s, int d) { const int x = s + d; return x >= R ? x - R : x; };
 
         bool ok = true;
@@ -341,7 +349,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const int kv_len = __ldg(it + 3);
             const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
             if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
-            tc_fence_after();
 
             int s = t % R;                      // slot and phase of the tile whose P V is issued next
             uint32_t ph = (t / R) & 1;
@@ -351,55 +358,72 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 const int s1 = slot_add(s, 1);
                 if (ok) ok = mbar_wait(bar_full_k + 8 * s, ph);
                 if (two && ok) ok = mbar_wait(bar_full_k + 8 * s1, s1 < s ? ph ^ 1 : ph);
+                ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
                 tc_fence_after();
-                if (!(p.debug & 4))
-#pragma unroll
-                for (int ks = 0; ks < kSteps; ++ks) {
-                    tc_mma(tmem_base + s * kTcTile, desc(q_lo + kstep_off(ks, 128)),
-                           desc(k_lo0 + s * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
-                    if (two)
-                        tc_mma(tmem_base + s1 * kTcTile, desc(q_lo + kstep_off(ks, 128)),
-                               desc(k_lo0 + s1 * kSlotStep + kstep_off(ks, kTcTile)), idesc_qk, ks > 0 ? 1u : 0u);
+                if (!(p.debug & 4)) {
+                    uint32_t q_w = q_lo, k_w = k_lo0 + s * kSlotStep, k_w1 = k_lo0 + s1 * kSlotStep, acc = 0;
+#pragma unroll 1
+                    for (int ks = 0; ks < kSteps; ++ks) {
+                        if (elect_one()) tc_mma(tmem_base + s * kTcTile, desc(q_w), desc(k_w), idesc_qk, acc);
+                        if (two && elect_one()) tc_mma(tmem_base + s1 * kTcTile, desc(q_w), desc(k_w1), idesc_qk, acc);
+                        const uint32_t step = (ks & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
+                        q_w += step;
+                        k_w += step;
+                        k_w1 += step;
+                        acc = 1;
+                    }
                 }
-                tc_commit(bar_s + 8 * s);
-                tc_commit(bar_empty_k + 8 * s);
+                if (elect_one()) tc_commit(bar_s + 8 * s);
+                if (elect_one()) tc_commit(bar_empty_k + 8 * s);
                 if (two) {
-                    tc_commit(bar_s + 8 * s1);
-                    tc_commit(bar_empty_k + 8 * s1);
+                    if (elect_one()) tc_commit(bar_s + 8 * s1);
+                    if (elect_one()) tc_commit(bar_empty_k + 8 * s1);
                 }
             }
             for (int j = 0; j < n_tiles; ++j, ++t) {
                 const bool have_a = j + 2 < n_tiles;
                 const int sa = slot_add(s, 2);
-                stamp(t, 7);
+                if (lane == 0) stamp(t, 7);
                 if (have_a && ok) ok = mbar_wait(bar_full_k + 8 * sa, sa < s ? ph ^ 1 : ph);
                 if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
                 if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(t) is in TMEM (over S(t))
+                ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
                 tc_fence_after();
-                stamp(t, 1);
+                if (lane == 0) stamp(t, 1);
                 // slot sa held tile t - 1, whose P V was issued in the previous iteration; MMAs
-                // execute in issue order, so S(t + 2) may overwrite it now
-                const uint32_t ka = k_lo0 + sa * kSlotStep, vs = v_lo0 + s * kSlotStep;
-                const uint32_t ta = tmem_base + sa * kTcTile, tp = tmem_base + s * kTcTile;
+                // execute in issue order, so S(t + 2) may overwrite it now.  The loop is kept rolled
+                // and small: this thread runs it once per tile between the softmax warps' much
+                // larger loops, and fetching its instructions is what its issue rate is bound by.
+                const bool qk = have_a && !(p.debug & 4), pv = !(p.debug & 8);
+                uint32_t q_w = q_lo, k_w = k_lo0 + sa * kSlotStep, v_w = v_lo0 + s * kSlotStep;
+                uint32_t p_col = tmem_base + s * kTcTile;
+                const uint32_t s_col = tmem_base + sa * kTcTile, o_col = tmem_base + tmem_o_col;
+                uint32_t acc_s = 0, acc_o = j > 0 ? 1u : 0u;
 #pragma unroll
                 for (int i = 0; i < kTcTile / 16; ++i) {
-                    if (i < kSteps && have_a && !(p.debug & 4))
-                        tc_mma(ta, desc(q_lo + kstep_off(i, 128)), desc(ka + kstep_off(i, kTcTile)), idesc_qk, i > 0 ? 1u : 0u);
-                    if (!(p.debug & 8))
-                        tc_mma_ts(tmem_base + tmem_o_col, tp + i * 8, desc(vs + i * (2048 >> 4)), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
+                    if (qk && i < kSteps && elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
+                    if (pv && elect_one()) tc_mma_ts(o_col, p_col, desc(v_w), idesc_pv, acc_o);
+                    // k-step i + 1 of a K-major operand of 128 rows: 32 B on, or into the next 64-element box
+                    const uint32_t step = (i & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
+                    q_w += step;
+                    k_w += step;
+                    v_w += 2048 >> 4;       // the next 16 tokens of V
+                    p_col += 8;             // 16 tokens of P = 8 packed columns
+                    acc_s = 1;
+                    acc_o = 1;
                 }
-                stamp(t, 6);
+                if (lane == 0) stamp(t, 6);
                 if (have_a) {
-                    tc_commit(bar_s + 8 * sa);
-                    tc_commit(bar_empty_k + 8 * sa);    // the K tile is free once this product has completed
+                    if (elect_one()) tc_commit(bar_s + 8 * sa);
+                    if (elect_one()) tc_commit(bar_empty_k + 8 * sa);    // the K tile is free once this product has completed
                 }
-                tc_commit(bar_o + 8 * s);
-                tc_commit(bar_empty_v + 8 * s);
-                stamp(t, 2);
+                if (elect_one()) tc_commit(bar_o + 8 * s);
+                if (elect_one()) tc_commit(bar_empty_v + 8 * s);
+                if (lane == 0) stamp(t, 2);
                 if (++s == R) { s = 0; ph ^= 1; }
             }
         }
-        if (!ok && p.status) atomicExch(p.status, 13);
+        if (!ok && lane == 0 && p.status) atomicExch(p.status, 13);
         return;
     }
 
@@ -476,6 +500,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 for (int i = 0; i < CH; ++i)
                     if (half * CH + i >= valid) sc[i] = -INFINITY;
             }
+            if (tid == 0) stamp(t, 8);
             float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
 #pragma unroll
             for (int i = 4; i < CH; i += 4) {
@@ -486,6 +511,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             xbuf[half * 128 + r] = fmaxf(mx0, mx1);
             pair_sync();
             const float mx = fmaxf(fmaxf(mx0, mx1), xbuf[(half ^ 1) * 128 + r]);
+            if (tid == 0) stamp(t, 9);
 
             const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
             if (j > 0 && __any_sync(kFullMask, raise)) {
@@ -517,8 +543,10 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 sum0 = static_cast<float>(CH);
             }
             l += sum0 + sum1;
+            if (tid == 0) stamp(t, 10);
             // P over the S columns this row has consumed: CH / 2 packed columns per half
             if (!(p.debug & 16)) tmem_st32(lane_addr + s * kTcTile + half * (CH / 2), packed);
+            if (tid == 0) stamp(t, 11);
             if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN

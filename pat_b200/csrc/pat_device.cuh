@@ -51,14 +51,19 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait: false if the phase did not complete within about kMaxWaitNs (or kMaxPolls
 // polls, whichever comes first).  The clock is only read every 256 polls.
 constexpr uint64_t kMaxWaitNs = 1000ull * 1000ull * 1000ull;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The polling loop is kept out of line: a kernel waits in many places, and warps that run a
+// little code per tile (TMA producers, the MMA issuer) are bound by instruction fetch.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
     const uint64_t start = global_timer_ns();
     for (uint32_t i = 1; i < kMaxPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0 && global_timer_ns() - start > kMaxWaitNs) return false;
     }
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity);
 }
 
 // ---- TMA: 4-D tiled load of one [16 tokens x 64 elements] box -----------------

@@ -268,7 +268,34 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         int64_t total_cost = 0;
         for (const DenseSeg& d : dsegs) total_cost += d.sg->tokens * passes(d);
         const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / (static_cast<int64_t>(kv_heads) * row_lanes));
-        const int64_t shares = std::min<int64_t>(max_shares, std::max<int64_t>(1, total_cost / min_piece));
+        int64_t share_limit = max_shares;
+        if (opt.dense_tile_ns > 0 && header_.stream_tokens > 0) {
+            // Both kernels run at the same time.  When the call is dominated by the streaming
+            // kernel's HBM traffic (about kStreamPsPerTokenHead per token and KV head: 512 bytes at
+            // 6.5 TB/s), the dense kernel - bound by the tensor and special-function units of the
+            // SMs it holds, not by memory - gets only the CTAs it needs to finish a little before
+            // the streaming kernel does; the streaming kernel fills the other SMs.  Short calls are
+            // bound by latencies this estimate knows nothing about: there the dense kernel is cut
+            // for every SM.
+            constexpr double kStreamPsPerTokenHead = 79.0, kWindowShare = 0.85, kMinWindowNs = 150e3;
+            constexpr double kItemNs = 8000.0, kFixedNs = 25000.0;   // per dense item (pipeline fill and drain), per launch
+            const double window_ns = static_cast<double>(header_.stream_tokens + header_.dense_unique_tokens) *
+                                     kv_heads * kStreamPsPerTokenHead * 1e-3;
+            if (window_ns >= kMinWindowNs) {
+                const int64_t group = static_cast<int64_t>(kv_heads) * row_lanes;      // CTAs per share
+                int64_t chunk_sum = 0;
+                for (const DenseSeg& d : dsegs) chunk_sum += d.chunks;
+                const double tile_ns = static_cast<double>(total_cost) * group / 128.0 * opt.dense_tile_ns;
+                for (int64_t sh = 1; sh < max_shares; ++sh) {
+                    const double items = static_cast<double>(chunk_sum * kv_heads + sh * group);
+                    if (kFixedNs + (tile_ns + items * kItemNs) / static_cast<double>(sh * group) <= kWindowShare * window_ns) {
+                        share_limit = sh;
+                        break;
+                    }
+                }
+            }
+        }
+        const int64_t shares = std::min<int64_t>(share_limit, std::max<int64_t>(1, total_cost / min_piece));
         struct Piece { const DenseSeg* d; int64_t pos, take; };
         std::vector<std::vector<Piece>> share_pieces(1);
         int64_t used = 0, assigned = 0;
