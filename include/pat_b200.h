@@ -163,8 +163,7 @@ const int32_t* pat_work_blob(const pat_work* w, size_t* words);
 enum { PAT_DTYPE_FP16 = 0, PAT_DTYPE_BF16 = 1 };
 enum { PAT_SKIP_STREAM = 1, PAT_SKIP_DENSE = 2, PAT_SKIP_MERGE = 4,
        PAT_DENSE_MMA_SYNC = 8, /* run the dense tiles on the legacy mma.sync kernel instead of tcgen05 */
-       PAT_NO_OVERLAP = 16     /* launch the dense kernel after the streaming kernel on the caller's stream,
-                                  not beside it on an internal stream */ };
+       PAT_NO_OVERLAP = 16     /* do not let the streaming kernel start while the dense kernel runs */ };
 
 typedef struct pat_decode_args {
     /* tensors (device pointers), strides in elements, last dimension contiguous */

@@ -59,40 +59,6 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 thread_local int g_last_launches = 0;
 constexpr int kMaxDevices = 64;
 
-// A second stream per (host thread, device) on which the dense kernel runs beside the streaming
-// kernel, with the two events that fork it from and join it to the caller's stream.  Created on
-// the first call that needs them; the event pattern is the one stream capture understands.
-struct SideStream {
-    cudaStream_t stream = nullptr;
-    cudaEvent_t fork = nullptr, join = nullptr;
-    ~SideStream() {
-        if (join) cudaEventDestroy(join);
-        if (fork) cudaEventDestroy(fork);
-        if (stream) cudaStreamDestroy(stream);
-    }
-};
-thread_local SideStream g_side[kMaxDevices];
-
-SideStream* side_stream(int dev) {
-    SideStream& s = g_side[dev];
-    if (s.stream) return &s;
-    int least = 0, greatest = 0;
-    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
-    cudaStream_t st = nullptr;
-    cudaEvent_t f = nullptr, j = nullptr;
-    if (cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, greatest) != cudaSuccess) return nullptr;
-    if (cudaEventCreateWithFlags(&f, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&j, cudaEventDisableTiming) != cudaSuccess) {
-        if (f) cudaEventDestroy(f);
-        cudaStreamDestroy(st);
-        return nullptr;
-    }
-    s.stream = st;
-    s.fork = f;
-    s.join = j;
-    return &s;
-}
-
 template <typename T, int D>
 int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     using namespace pat;
@@ -131,17 +97,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     const bool dense_tc = dense && !(a.flags & PAT_DENSE_MMA_SYNC);
 
     // The streaming kernel is bound by HBM, the dense kernel by the tensor and special-function
-    // units of the SMs it holds and it needs few of them when the work list sized it so
-    // (num_dense_ctas below the SM count).  So the dense kernel goes first, on a side stream, and
-    // the streaming kernel fills the SMs it leaves - and takes them over as its CTAs retire.
-    SideStream* side = nullptr;
-    if (streaming && dense_tc && !(a.flags & PAT_NO_OVERLAP)) {
-        side = side_stream(dev);
-        if (!side) return PAT_ERR_CUDA;
-        if (cudaEventRecord(side->fork, stream) != cudaSuccess ||
-            cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
-            return PAT_ERR_CUDA;
-    }
+    // units of the SMs it holds, and it needs few of them when the work list sized it so
+    // (num_dense_ctas below the SM count).  So the dense kernel is launched first and the
+    // streaming kernel as its programmatic dependent: it may start as soon as every dense CTA is
+    // running (each signals that at its top; the streaming kernel never waits for the dense
+    // kernel's results), fills the SMs the dense kernel leaves and takes the others over as the
+    // dense CTAs retire.  The merge kernel is an ordinary launch and waits for both.
+    const bool overlap = streaming && dense_tc && !(a.flags & PAT_NO_OVERLAP);
     if (dense_tc) {
         // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
         static bool configured[kMaxDevices] = {};
@@ -158,7 +120,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         DenseTcParams dp{};
         dp.a = pd;
         dp.cta_begin = a.work_blob + a.work.dense_cta_off;
-        kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, side ? side->stream : stream>>>(dp, kmap, vmap);
+        kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, stream>>>(dp, kmap, vmap);
         ++launches;
     }
     if (streaming) {
@@ -174,13 +136,18 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         p.num_items = a.work.num_stream_items;
         const long long grid = static_cast<long long>(p.num_items) * a.num_kv_heads;
         if (grid > 0x7fffffffLL) return PAT_ERR_TOO_LARGE;
-        kern<<<static_cast<unsigned>(grid), kStreamWarps * 32, smem, stream>>>(p, kmap, vmap);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(grid));
+        cfg.blockDim = dim3(kStreamWarps * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = overlap ? 1 : 0;
+        if (cudaLaunchKernelEx(&cfg, kern, p, kmap, vmap) != cudaSuccess) return PAT_ERR_CUDA;
         ++launches;
-    }
-    if (side) {
-        if (cudaEventRecord(side->join, side->stream) != cudaSuccess ||
-            cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess)
-            return PAT_ERR_CUDA;
     }
     if (dense && !dense_tc) {
         // the same items on the legacy mma.sync path (kept for comparison): one CTA per
@@ -315,6 +282,5 @@ extern "C" int pat_b200_decode_static_scratch(const pat_decode_args* args, void*
     pat_decode_args local = *args;
     local.workspace = ptr;
     local.workspace_bytes = PAT_B200_STATIC_SCRATCH_BYTES;
-    local.flags |= PAT_NO_OVERLAP;      // no side stream: this entry point creates nothing
     return pat_b200_decode(&local, stream_handle);
 }

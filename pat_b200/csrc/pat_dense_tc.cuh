@@ -232,6 +232,9 @@ struct DenseTcParams {
 template <typename T, int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    // This CTA is running: a kernel launched as this one's programmatic dependent (the streaming
+    // kernel, which does not use this kernel's results) may start once every CTA has said so.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     using L = TcSmem<D>;
     constexpr int R = kTcRing;
     constexpr int kSW = kTcSoftmaxWarps;        // warps 0..7 softmax, 8 = K producer, 9 = MMA, 10 = V producer
