@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA graph replays")
+    ap.add_argument("--emulate-shards", type=int, default=0,
+                    help="with one GPU: run the work one rank of an S-GPU run would get (S KV-head shards)")
     ap.add_argument("--flags", type=int, default=0, help="extra launch flags (include/pat_b200.h), e.g. 16 = no overlap")
     ap.add_argument("--scale-down", type=int, default=1,
                     help="divide every segment length by this factor (profiling captures on a small case)")
@@ -149,18 +151,19 @@ def main():
 
     from pat_b200.workloads import make_config, scaled_down, torch_dtype
     w = make_config(args.config) if args.scale_down <= 1 else scaled_down(args.config, args.scale_down)
-    if w.num_kv_heads % n != 0:
+    if w.num_kv_heads % n != 0 or (args.emulate_shards > 1 and w.num_kv_heads % args.emulate_shards != 0):
         if rank == 0:
             print(json.dumps({"metric": METRIC, "unavailable": f"{w.num_kv_heads} KV heads do not shard over {n} GPUs"}))
         return
-    hk = w.num_kv_heads // n
+    shards = args.emulate_shards if (n == 1 and args.emulate_shards > 1) else n
+    hk = w.num_kv_heads // shards
     hq = hk * w.group
     D, page, B = w.head_dim, w.page_size, w.batch
     scale = 1.0 / math.sqrt(D)
     dt = torch_dtype(w.dtype)
     workload_name = f"{w.name}: {w.description}; {w.num_q_heads}/{w.num_kv_heads} heads, D={D}, {w.dtype}, {page}-token pages"
     config = {"workload": workload_name, "batch": B, "unique_tokens": w.unique_tokens,
-              "total_tokens": w.total_tokens, "kv_head_shards": n,
+              "total_tokens": w.total_tokens, "kv_head_shards": shards,
               "l2": "inputs larger than L2 (per-GPU KV bytes >> 126 MB); no flush between steps"}
     bytes_total = w.dedup_kv_bytes()
     bytes_rank = w.dedup_kv_bytes(kv_heads=hk, q_heads=hq)

@@ -44,7 +44,7 @@ struct AttnParams {
     int debug;            // experiment switches (flags >> 8); 0 in normal use
 };
 
-constexpr int kStreamWarps = 4;
+constexpr int kStreamWarps = 3;
 constexpr int kStreamStages = 3;
 constexpr int kDenseWarps = 8;          // consumer warps (16 rows each)
 constexpr int kDenseStages = 3;
