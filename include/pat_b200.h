@@ -26,7 +26,7 @@ typedef enum pat_status {
     PAT_ERR_NOT_BUILT = -5,
     PAT_ERR_BAD_PLAN = -10,          /* plan tables inconsistent (index out of range ...) */
     PAT_ERR_UNSUPPORTED = -11,       /* dtype / head_dim / head ratio / alignment not supported */
-    PAT_ERR_WORKSPACE = -12,         /* workspace too small or missing */
+    PAT_ERR_WORKSPACE = -12,         /* workspace missing, too small or not 32-byte aligned */
     PAT_ERR_CUDA = -13,              /* a CUDA runtime or driver call failed */
     PAT_ERR_NO_DEVICE_CODE = -14,    /* the GPU is not an sm_100 part */
     PAT_ERR_TOO_LARGE = -15          /* size beyond a fixed limit */
@@ -186,7 +186,7 @@ typedef struct pat_decode_args {
     /* work list */
     const int32_t* work_blob;   /* device copy of pat_work_blob */
     pat_work_header work;       /* host copy of the header */
-    /* scratch for the per-(item, query) partial results */
+    /* scratch for the per-(item, query, KV head) partial results; 32-byte aligned */
     void* workspace;
     size_t workspace_bytes;
     /* optional device int32[4]: [0] != 0 after the call means a bounded wait gave up */

@@ -229,7 +229,9 @@ int pat_b200_decode(const pat_decode_args* args, void* stream_handle) {
         if (s <= 0 || s % 8 != 0) return PAT_ERR_UNSUPPORTED;
     if (!aligned16(a.work_blob)) return PAT_ERR_BAD_ARGUMENT;
     const size_t need = pat_b200_workspace_bytes(&a.work, a.num_q_heads, a.head_dim);
-    if (a.work.num_entries > 0 && (!a.workspace || a.workspace_bytes < need || !aligned16(a.workspace)))
+    // the dense kernel writes its partial rows with 32-byte stores
+    if (a.work.num_entries > 0 && (!a.workspace || a.workspace_bytes < need ||
+                                   (reinterpret_cast<uintptr_t>(a.workspace) & 31) != 0))
         return PAT_ERR_WORKSPACE;
 
     int dev = 0;

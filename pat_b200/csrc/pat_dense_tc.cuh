@@ -249,11 +249,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     const uint32_t sQ = base + L::kQOff, sK = base + L::kKOff, sV = base + L::kVOff;
     const uint32_t bars = base + L::kBarOff;
     // barrier map (8 bytes each): full_k[R] empty_k[R] full_v[R] empty_v[R] s_full[R] p_ready[R]
-    // o_done[R] q_ready
+    // o_done[R] q_ready o_free
     const uint32_t bar_full_k = bars, bar_empty_k = bars + 8 * R, bar_full_v = bars + 16 * R, bar_empty_v = bars + 24 * R,
-                   bar_s = bars + 32 * R, bar_p = bars + 40 * R, bar_o = bars + 48 * R, bar_q = bars + 56 * R;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 56 * R + 8);
-    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 56 * R + 16);
+                   bar_s = bars + 32 * R, bar_p = bars + 40 * R, bar_o = bars + 48 * R, bar_q = bars + 56 * R,
+                   bar_ofree = bars + 56 * R + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 56 * R + 16);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 56 * R + 24);
     float* xch = reinterpret_cast<float*>(tc_smem + L::kXchOff);      // [2][2][128]
 
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
@@ -272,6 +273,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         for (int i = 0; i < R; ++i) mbar_init(bar_p + 8 * i, kSW * 32);         // p_ready: every softmax thread
         for (int i = 0; i < R; ++i) mbar_init(bar_o + 8 * i, 1);                // o_done
         mbar_init(bar_q, kSW * 32);                                             // q_ready
+        mbar_init(bar_ofree, kSW * 32);                                         // o_free
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTcTmemCols);
@@ -345,66 +347,75 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kHi) << 32) | lo; };
         auto slot_add = [](int s, int d) { const int x = s + d; return x >= R ? x - R : x; };
 
+        // The CTA's items form one stream of tiles g = 0, 1, ...: S(g + 2) is requested while tile g
+        // is multiplied into O, across item boundaries too, so that a new item costs no pipeline
+        // fill.  Two cursors walk the item list: one for the Q K^T products, two tiles ahead of the
+        // one for the P V products.
         bool ok = true;
-        int t = 0, n_item = 0;                  // t: running tile index over all items
-        for (int item = item_lo; item < item_hi; ++item, ++n_item) {
-            const int32_t* it = p.items + static_cast<size_t>(item) * 8;
-            const int kv_len = __ldg(it + 3);
-            const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
-            if (ok) ok = mbar_wait(bar_q, n_item & 1);                 // this item's Q rows are in place
-
-            int s = t % R;                      // slot and phase of the tile whose P V is issued next
-            uint32_t ph = (t / R) & 1;
-            // prologue: S(0) and S(1)
-            {
-                const bool two = n_tiles > 1;
-                const int s1 = slot_add(s, 1);
-                if (ok) ok = mbar_wait(bar_full_k + 8 * s, ph);
-                if (two && ok) ok = mbar_wait(bar_full_k + 8 * s1, s1 < s ? ph ^ 1 : ph);
-                ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
-                tc_fence_after();
-                if (!(p.debug & 4)) {
-                    uint32_t q_w = q_lo, k_w = k_lo0 + s * kSlotStep, k_w1 = k_lo0 + s1 * kSlotStep, acc = 0;
-#pragma unroll 1
-                    for (int ks = 0; ks < kSteps; ++ks) {
-                        if (elect_one()) tc_mma(tmem_base + s * kTcTile, desc(q_w), desc(k_w), idesc_qk, acc);
-                        if (two && elect_one()) tc_mma(tmem_base + s1 * kTcTile, desc(q_w), desc(k_w1), idesc_qk, acc);
-                        const uint32_t step = (ks & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
-                        q_w += step;
-                        k_w += step;
-                        k_w1 += step;
-                        acc = 1;
-                    }
-                }
-                if (elect_one()) tc_commit(bar_s + 8 * s);
-                if (elect_one()) tc_commit(bar_empty_k + 8 * s);
-                if (two) {
-                    if (elect_one()) tc_commit(bar_s + 8 * s1);
-                    if (elect_one()) tc_commit(bar_empty_k + 8 * s1);
+        auto tiles_of = [&](int item) {
+            return item < item_hi ? (__ldg(p.items + static_cast<size_t>(item) * 8 + 3) + kTcTile - 1) / kTcTile : 0;
+        };
+        int total_tiles = 0;
+        for (int item = item_lo; item < item_hi; ++item) total_tiles += tiles_of(item);
+        int qk_item = item_lo, qk_j = 0, qk_n = tiles_of(item_lo), qk_items = 0;     // cursor of the next Q K^T
+        int pv_j = 0, pv_n = qk_n, pv_item = item_lo, pv_items = 0;                  // cursor of the next P V
+        auto qk_advance = [&]() {
+            if (++qk_j == qk_n) { ++qk_item; qk_j = 0; qk_n = tiles_of(qk_item); }
+        };
+        // S(tile at the cursor) = Q K^T into ring slot `slot`; on its own (not interleaved)
+        auto qk_alone = [&](int slot, uint32_t phase) {
+            if (qk_j == 0) {            // a new item: its Q rows must be in shared memory
+                if (ok) ok = mbar_wait(bar_q, qk_items & 1);
+                ++qk_items;
+            }
+            if (ok) ok = mbar_wait(bar_full_k + 8 * slot, phase);
+            ok = __all_sync(kFullMask, ok);
+            tc_fence_after();
+            if (!(p.debug & 4)) {
+                uint32_t q_w = q_lo, k_w = k_lo0 + slot * kSlotStep, acc = 0;
+#pragma unroll
+                for (int ks = 0; ks < kSteps; ++ks) {
+                    if (elect_one()) tc_mma(tmem_base + slot * kTcTile, desc(q_w), desc(k_w), idesc_qk, acc);
+                    const uint32_t step = (ks & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
+                    q_w += step;
+                    k_w += step;
+                    acc = 1;
                 }
             }
-            for (int j = 0; j < n_tiles; ++j, ++t) {
-                const bool have_a = j + 2 < n_tiles;
-                const int sa = slot_add(s, 2);
-                if (lane == 0) stamp(t, 7);
-                if (have_a && ok) ok = mbar_wait(bar_full_k + 8 * sa, sa < s ? ph ^ 1 : ph);
-                if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
-                if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(t) is in TMEM (over S(t))
-                ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
-                tc_fence_after();
-                if (lane == 0) stamp(t, 1);
-                // slot sa held tile t - 1, whose P V was issued in the previous iteration; MMAs
-                // execute in issue order, so S(t + 2) may overwrite it now.  The loop is kept rolled
-                // and small: this thread runs it once per tile between the softmax warps' much
-                // larger loops, and fetching its instructions is what its issue rate is bound by.
-                const bool qk = have_a && !(p.debug & 4), pv = !(p.debug & 8);
+            if (elect_one()) tc_commit(bar_s + 8 * slot);
+            if (elect_one()) tc_commit(bar_empty_k + 8 * slot);    // the K tile is free once this product has completed
+            qk_advance();
+        };
+        int s = 0;                              // ring slot and phase of tile g
+        uint32_t ph = 0;
+        qk_alone(0, 0);
+        if (total_tiles > 1) qk_alone(1, 0);
+        for (int g = 0; g < total_tiles; ++g) {
+            const bool have_a = g + 2 < total_tiles;
+            const bool a_new_item = have_a && qk_j == 0;       // S(g + 2) opens an item: issued after P V(g)
+            const bool qk = have_a && !a_new_item;
+            const int sa = slot_add(s, 2);
+            const uint32_t pha = sa < s ? ph ^ 1 : ph;
+            if (lane == 0) stamp(g, 7);
+            if (qk && ok) ok = mbar_wait(bar_full_k + 8 * sa, pha);
+            if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
+            if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(g) is in TMEM (over S(g))
+            if (pv_j == 0 && pv_items > 0 && ok)
+                ok = mbar_wait(bar_ofree, (pv_items - 1) & 1);     // the softmax warps have read the previous item's O
+            ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
+            tc_fence_after();
+            if (lane == 0) stamp(g, 1);
+            // slot sa held tile g - 1, whose P V was issued in the previous iteration; MMAs execute in
+            // issue order, so S(g + 2) may overwrite it now
+            {
+                const bool do_qk = qk && !(p.debug & 4), pv = !(p.debug & 8);
                 uint32_t q_w = q_lo, k_w = k_lo0 + sa * kSlotStep, v_w = v_lo0 + s * kSlotStep;
                 uint32_t p_col = tmem_base + s * kTcTile;
                 const uint32_t s_col = tmem_base + sa * kTcTile, o_col = tmem_base + tmem_o_col;
-                uint32_t acc_s = 0, acc_o = j > 0 ? 1u : 0u;
+                uint32_t acc_s = 0, acc_o = pv_j > 0 ? 1u : 0u;
 #pragma unroll
                 for (int i = 0; i < kTcTile / 16; ++i) {
-                    if (qk && i < kSteps && elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
+                    if (do_qk && i < kSteps && elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
                     if (pv && elect_one()) tc_mma_ts(o_col, p_col, desc(v_w), idesc_pv, acc_o);
                     // k-step i + 1 of a K-major operand of 128 rows: 32 B on, or into the next 64-element box
                     const uint32_t step = (i & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
@@ -415,16 +426,20 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                     acc_s = 1;
                     acc_o = 1;
                 }
-                if (lane == 0) stamp(t, 6);
-                if (have_a) {
-                    if (elect_one()) tc_commit(bar_s + 8 * sa);
-                    if (elect_one()) tc_commit(bar_empty_k + 8 * sa);    // the K tile is free once this product has completed
-                }
-                if (elect_one()) tc_commit(bar_o + 8 * s);
-                if (elect_one()) tc_commit(bar_empty_v + 8 * s);
-                if (lane == 0) stamp(t, 2);
-                if (++s == R) { s = 0; ph ^= 1; }
             }
+            if (lane == 0) stamp(g, 6);
+            if (qk) {
+                if (elect_one()) tc_commit(bar_s + 8 * sa);
+                if (elect_one()) tc_commit(bar_empty_k + 8 * sa);
+                qk_advance();
+            }
+            if (elect_one()) tc_commit(bar_o + 8 * s);
+            if (elect_one()) tc_commit(bar_empty_v + 8 * s);
+            if (lane == 0) stamp(g, 2);
+            if (++pv_j == pv_n) { ++pv_item; ++pv_items; pv_j = 0; pv_n = tiles_of(pv_item); }
+            if (a_new_item) qk_alone(sa, pha);  // waits for the next item's Q, which the softmax warps
+                                                // write once they have seen the last S of this item
+            if (++s == R) { s = 0; ph ^= 1; }
         }
         if (!ok && lane == 0 && p.status) atomicExch(p.status, 13);
         return;
@@ -455,6 +470,31 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         tc_fence_after();
     };
     auto pair_sync = [&]() { named_bar_sync(2 + quad, 64); };   // the two warps that share TMEM lanes
+    // Q rows of an item, half a row per thread: global -> registers, registers -> the swizzled
+    // K-major layout in shared memory (the address takes two dependent loads, so it is worked
+    // out an item ahead)
+    auto q_addr = [&](int item) -> const uint4* {
+        const int32_t* it = p.items + static_cast<size_t>(item) * 8;
+        const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kvh = __ldg(it + 5);
+        if (r >= nq * p.hratio) return nullptr;
+        const int qi = r / p.hratio, gg = r - qi * p.hratio;
+        const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
+                     static_cast<int64_t>(kvh * p.hratio + gg) * p.q_head_stride;
+        return reinterpret_cast<const uint4*>(q) + half * (D / 16);
+    };
+    auto q_fetch = [&](const uint4* src, uint4 (&qv)[D / 16]) {
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) qv[i] = src ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+    };
+    auto q_store = [&](const uint4 (&qv)[D / 16]) {
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            const int ch = half * (D / 16) + i;
+            const uint32_t dst = sQ + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(qv[i].x), "r"(qv[i].y), "r"(qv[i].z), "r"(qv[i].w) : "memory");
+        }
+        fence_async_smem();
+    };
     for (int item = item_lo; item < item_hi; ++item) {
         const int32_t* it = p.items + static_cast<size_t>(item) * 8;
         const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kv_len = __ldg(it + 3), entry_base = __ldg(it + 4),
@@ -462,33 +502,35 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const int rows_valid = nq * p.hratio;
         const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
 
-        // Q rows of this item into the swizzled K-major layout, half a row per thread (every MMA of
-        // the previous item has completed: its last o_done was consumed in the epilogue below)
-        {
-            const uint4* src = nullptr;
-            if (r < rows_valid) {
-                const int qi = r / p.hratio, gg = r - qi * p.hratio;
-                const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
-                             static_cast<int64_t>(kvh * p.hratio + gg) * p.q_head_stride;
-                src = reinterpret_cast<const uint4*>(q);
-            }
-#pragma unroll
-            for (int i = 0; i < D / 16; ++i) {
-                const int ch = half * (D / 16) + i;
-                const uint4 v = src ? __ldg(src + ch) : make_uint4(0, 0, 0, 0);
-                const uint32_t dst = sQ + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-            }
-            fence_async_smem();
+        // the first item's Q rows; those of every later item are written during the last tile of the
+        // item before it (below)
+        if (item == item_lo) {
+            uint4 qv[D / 16];
+            q_fetch(q_addr(item), qv);
+            q_store(qv);
+            tc_fence_before();
+            mbar_arrive(bar_q);
         }
-        tc_fence_before();
-        mbar_arrive(bar_q);
 
+        const uint4* q_next = item + 1 < item_hi ? q_addr(item + 1) : nullptr;
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j, ++t) {
             if (tid == 0) stamp(t, 3);
-            if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
-            tc_fence_after();
+            if (j == n_tiles - 1 && item + 1 < item_hi) {
+                // Last tile of the item.  Once its S has completed, so has every Q K^T of the item,
+                // and the Q rows of the next item can take their place: the MMA warp then requests
+                // that item's first S tiles while this item is still being finished.
+                uint4 qv[D / 16];
+                q_fetch(q_next, qv);            // in flight during the wait
+                if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
+                tc_fence_after();
+                q_store(qv);
+                tc_fence_before();
+                mbar_arrive(bar_q);
+            } else {
+                if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
+                tc_fence_after();
+            }
             if (tid == 0) stamp(t, 4);
             constexpr int CH = kTcTile / 2;     // token columns per thread
             float sc[CH];
@@ -593,11 +635,19 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const float inv = 1.f / l_row;
             float ov[OC];
             tmem_ld_f<OC>(tmem_o, ov);
+            tc_fence_before();
+            mbar_arrive(bar_ofree);             // O may be overwritten by the next item's first P V
             if (store) {
-                float4* dst = reinterpret_cast<float4*>(p.part_o + slot * D + half * OC);
+                // 32 bytes per store: the rows of a warp lie D floats apart, so every store instruction
+                // touches 32 lines whatever its width, and the wide form halves their number
+                float* dst = p.part_o + slot * D + half * OC;
 #pragma unroll
-                for (int i = 0; i < OC / 4; ++i)
-                    dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+                for (int i = 0; i < OC / 8; ++i)
+                    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                 ::"l"(dst + 8 * i), "f"(ov[8 * i] * inv), "f"(ov[8 * i + 1] * inv), "f"(ov[8 * i + 2] * inv),
+                                   "f"(ov[8 * i + 3] * inv), "f"(ov[8 * i + 4] * inv), "f"(ov[8 * i + 5] * inv),
+                                   "f"(ov[8 * i + 6] * inv), "f"(ov[8 * i + 7] * inv)
+                                 : "memory");
                 if (half == 0) p.part_lse[slot] = m_used * p.scale + logf(l_row);
             }
         }

@@ -403,8 +403,17 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
     const int lo = __ldg(p.indptr + list), n = __ldg(p.indptr + list + 1) - lo;
     const int32_t* ent = p.entries + lo;
 
-    float gmax = -INFINITY;
-    for (int i = lane; i < n; i += 32)
+    // Lane i owns entry i (and i + 32, ...): its slot and LSE are loaded side by side, then the
+    // partial rows are read four at a time (independent loads), the slot and weight of each
+    // coming from the owning lane by shuffle.  A list rarely has more than 32 entries.
+    size_t my_slot = 0;
+    float my_lse = -INFINITY;
+    if (lane < n) {
+        my_slot = static_cast<size_t>(__ldg(ent + lane)) * p.hratio + g;
+        my_lse = __ldg(p.part_lse + my_slot);
+    }
+    float gmax = my_lse;
+    for (int i = lane + 32; i < n; i += 32)
         gmax = fmaxf(gmax, __ldg(p.part_lse + static_cast<size_t>(__ldg(ent + i)) * p.hratio + g));
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(kFullMask, gmax, d));
@@ -413,18 +422,45 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
 #pragma unroll
     for (int k = 0; k < kPer; ++k) acc[k] = 0.f;
     float wsum = 0.f;
-    for (int i = 0; i < n; ++i) {
-        const size_t slot = static_cast<size_t>(__ldg(ent + i)) * p.hratio + g;
-        const float lse = __ldg(p.part_lse + slot);
-        const float w = (lse == -INFINITY) ? 0.f : __expf(lse - gmax);
-        wsum += w;
-        const float* src = p.part_o + slot * D + lane * kPer;
-        if constexpr (kPer == 4) {
-            const float4 x = __ldg(reinterpret_cast<const float4*>(src));
-            acc[0] += w * x.x; acc[1] += w * x.y; acc[2] += w * x.z; acc[3] += w * x.w;
-        } else {
-            const float2 x = __ldg(reinterpret_cast<const float2*>(src));
-            acc[0] += w * x.x; acc[1] += w * x.y;
+    for (int base = 0; base < n; base += 32) {
+        if (base > 0) {
+            my_slot = 0;
+            my_lse = -INFINITY;
+            if (base + lane < n) {
+                my_slot = static_cast<size_t>(__ldg(ent + base + lane)) * p.hratio + g;
+                my_lse = __ldg(p.part_lse + my_slot);
+            }
+        }
+        const float my_w = (my_lse == -INFINITY) ? 0.f : __expf(my_lse - gmax);    // 0 for lanes past the list
+        const int cnt = min(32, n - base);
+        const unsigned slot_lo = static_cast<unsigned>(my_slot), slot_hi = static_cast<unsigned>(my_slot >> 32);
+        for (int i = 0; i < cnt; i += 4) {
+            float w[4];
+            float4 x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                // lanes past the list hold slot 0 and weight 0: a valid address, no contribution
+                const int src_lane = min(i + k, 31);
+                const size_t slot = (static_cast<size_t>(__shfl_sync(kFullMask, slot_hi, src_lane)) << 32) |
+                                    __shfl_sync(kFullMask, slot_lo, src_lane);
+                w[k] = (i + k < cnt) ? __shfl_sync(kFullMask, my_w, src_lane) : 0.f;
+                const float* src = p.part_o + slot * D + lane * kPer;
+                if constexpr (kPer == 4) {
+                    x[k] = __ldg(reinterpret_cast<const float4*>(src));
+                } else {
+                    const float2 y = __ldg(reinterpret_cast<const float2*>(src));
+                    x[k] = make_float4(y.x, y.y, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (w[k] != 0.f) {      // a skipped row may hold anything (never written slots are not read: w = 0)
+                    wsum += w[k];
+                    acc[0] += w[k] * x[k].x;
+                    acc[1] += w[k] * x[k].y;
+                    if constexpr (kPer == 4) { acc[2] += w[k] * x[k].z; acc[3] += w[k] * x[k].w; }
+                }
+            }
         }
     }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
