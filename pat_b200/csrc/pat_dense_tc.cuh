@@ -617,15 +617,18 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         }
 
         // ---- item epilogue: O / l -> fp32 partial, LSE ---------------------------------------------
-        ensure_o(t);
         {
-            // row sum = the two halves' sums (same buffer discipline as the maxima: parity of t)
+            // row sum = the two halves' sums (same buffer discipline as the maxima: parity of t);
+            // exchanged while the last P V is still on its way
             float* xbuf = xch + (t & 1) * 256;
             pair_sync();                        // partner has read the last tile's maximum
             xbuf[half * 128 + r] = l;
             pair_sync();
             const float l_row = l + xbuf[(half ^ 1) * 128 + r];
             pair_sync();                        // both have read before the buffer is reused
+            if (tid == 0) stamp(t - 1, 12);
+            ensure_o(t);
+            if (tid == 0) stamp(t - 1, 13);
             const bool store = ok && r < rows_valid;
             size_t slot = 0;
             if (r < rows_valid) {
@@ -637,6 +640,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             tmem_ld_f<OC>(tmem_o, ov);
             tc_fence_before();
             mbar_arrive(bar_ofree);             // O may be overwritten by the next item's first P V
+            if (tid == 0) stamp(t - 1, 14);
             if (store) {
                 // 32 bytes per store: the rows of a warp lie D floats apart, so every store instruction
                 // touches 32 lines whatever its width, and the wide form halves their number
@@ -650,6 +654,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                                  : "memory");
                 if (half == 0) p.part_lse[slot] = m_used * p.scale + logf(l_row);
             }
+            if (tid == 0) stamp(t - 1, 15);
         }
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
