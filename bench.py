@@ -168,7 +168,7 @@ def main():
     bytes_total = w.dedup_kv_bytes()
     bytes_rank = w.dedup_kv_bytes(kv_heads=hk, q_heads=hq)
     if bytes_rank < 4 * 126e6:
-        config["l2"] = "per-GPU KV bytes are below 4x L2: a 512 MB buffer is written between steps to flush L2"
+        config["l2"] = "per-GPU KV bytes are below 4x L2: between steps a 512 MB buffer is written and a 256 MB buffer read to flush L2"
 
     # ------------------------------------------------------------------ reference arm (CPU)
     if args.impl == "reference":
@@ -243,9 +243,13 @@ def main():
     work = tree.kernel_info.device_work(dev)
     hdr = work.header
 
-    flush = None
+    # L2 flush for the small workloads: write a buffer larger than L2, then read another one, so that
+    # the timed step starts with an L2 that holds none of its inputs and no dirty lines of the
+    # flush itself (their write-back would otherwise run during the timed step).
+    flush = flush_rd = None
     if bytes_rank < 4 * 126e6:
         flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+        flush_rd = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
 
     def step(flags=0):
         prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags | args.flags)
@@ -262,6 +266,7 @@ def main():
         for a, b in evs:
             if flush is not None:
                 flush.fill_(1)
+                flush_rd.max()
             a.record()
             fn()
             b.record()
@@ -370,6 +375,12 @@ def main():
     else:
         alg = hdr.num_entries * w.group * (D + 1) * 4 + B * hq * D * elt
     achieved = alg / (k_ms[dominant] * 1e-3) / 1e9
+    # DRAM traffic per launch: dram__bytes_read + dram__bytes_write of one ncu capture of the same
+    # kernels on this workload with all lengths / 4 (profiles/stream_dense_merge_cfg4_div4_full.md),
+    # as a ratio to the algorithmic bytes of that launch, scaled to this launch (the traffic of
+    # both kernels grows in proportion to the tokens they read).  Other workloads: not captured.
+    ncu_traffic_ratio = {"stream_kernel": 939.8 / 917.8, "dense_kernel": 127.8 / 117.4}
+    traffic = int(alg * ncu_traffic_ratio[dominant]) if (args.config == 4 and dominant in ncu_traffic_ratio) else None
     step_gbs = bytes_rank / (ms * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": ms * 1e3, "unit": UNIT, "n_gpus": n, "steps": args.steps,
@@ -381,7 +392,7 @@ def main():
                 "d2h_bytes_per_step": int(out_host.numel() * elt)},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
                      "algorithmic_bytes_per_launch": alg, "kernel_ms": k_ms[dominant]},
         "step_roofline": {"dedup_bytes_per_gpu": bytes_rank, "dedup_bytes_total": bytes_total,
                           "achieved_gbs_per_gpu": step_gbs, "frac_of_measured_copy": step_gbs / peak,

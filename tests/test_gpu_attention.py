@@ -134,6 +134,26 @@ def test_benchmark_configs_full_sampled(cfg, sample, native_lib):
     assert (lse - lse2).abs().max().item() <= 1e-3
 
 
+def test_dense_kernel_beside_the_streaming_kernel(native_lib):
+    """cfg4 at full size is long enough for the work list to give the dense kernel only a share
+    of the SMs and run it beside the streaming kernel.  The result must be bit-identical when the
+    streaming kernel is an ordinary launch instead (flag PAT_NO_OVERLAP = 16: same work list, same
+    arithmetic, only the launch order differs), and agree with the all-SM cut of the dense work."""
+    w = make_config(4)
+    q, k, v = make_values(w)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    args = (q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale)
+    out, lse, tree = _run_tree(*args)
+    hdr = tree.kernel_info.device_work(torch.device(DEV)).header
+    assert 0 < hdr.num_dense_ctas < 100 and hdr.num_stream_items > 0
+    serial, lse_s, _ = _run_tree(*args, flags=16)
+    assert torch.equal(out, serial) and torch.equal(lse, lse_s)
+    wide, lse_w, tree_w = _run_tree(*args, cfg=P.WorkConfig(dense_tile_ns=-1))
+    assert tree_w.kernel_info.device_work(torch.device(DEV), P.WorkConfig(dense_tile_ns=-1)).header.num_dense_ctas > hdr.num_dense_ctas
+    assert (out - wide).abs().max().item() <= TOL[torch.bfloat16]
+    assert (lse - lse_w).abs().max().item() <= 1e-3
+
+
 @pytest.mark.parametrize("cfg,factor", [(3, 4), (4, 32)])
 def test_scaled_configs_all_requests(cfg, factor, native_lib):
     w = scaled_down(cfg, factor)
