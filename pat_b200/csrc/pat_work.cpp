@@ -86,20 +86,45 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
     // Signatures are kept as linked lists in a flat pool; their hash is updated
     // as boxes are appended (boxes are visited in increasing order, so equal
     // sets give equal sequences).
-    std::unordered_map<uint64_t, int> slot_of;   // (page << 32 | valid) -> slot
+    // Full pages (all but the last page of a box, at most) are looked up in a flat table indexed
+    // by page id; only partial pages go through the hash map.
+    std::unordered_map<uint64_t, int> slot_of;   // (page << 32 | valid) -> slot, partial pages
     std::vector<uint64_t> slot_key, slot_hash;
     std::vector<int> slot_head, slot_tail, slot_len;
     std::vector<int> link_box, link_next;
-    slot_of.reserve(1024);
+    size_t total_links = 0;
+    int32_t max_page = -1;
+    for (const FusedBox& f : fused) {
+        total_links += static_cast<size_t>(f.num_pages);
+        for (int p = 0; p < f.num_pages; ++p) max_page = std::max(max_page, f.pages[p]);
+    }
+    std::vector<int> full_slot(static_cast<size_t>(max_page) + 1, -1);
+    slot_key.reserve(total_links);
+    slot_hash.reserve(total_links);
+    slot_head.reserve(total_links);
+    slot_tail.reserve(total_links);
+    slot_len.reserve(total_links);
+    link_box.reserve(total_links);
+    link_next.reserve(total_links);
     for (int g = 0; g < static_cast<int>(fused.size()); ++g) {
         const FusedBox& f = fused[g];
         for (int p = 0; p < f.num_pages; ++p) {
             const int valid = (p == f.num_pages - 1) ? f.kv_len - p * page_size : page_size;
             const uint64_t key = (static_cast<uint64_t>(static_cast<uint32_t>(f.pages[p])) << 32) |
                                  static_cast<uint32_t>(valid);
-            auto ins = slot_of.emplace(key, static_cast<int>(slot_key.size()));
-            int s = ins.first->second;
-            if (ins.second) {
+            int s;
+            bool fresh;
+            if (valid == page_size) {
+                int& ref = full_slot[f.pages[p]];
+                fresh = ref < 0;
+                if (fresh) ref = static_cast<int>(slot_key.size());
+                s = ref;
+            } else {
+                auto ins = slot_of.emplace(key, static_cast<int>(slot_key.size()));
+                s = ins.first->second;
+                fresh = ins.second;
+            }
+            if (fresh) {
                 slot_key.push_back(key);
                 slot_hash.push_back(0x9876);
                 slot_head.push_back(-1);
@@ -130,30 +155,40 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         }
         return true;
     };
+    int last_seg = -1;
+    uint64_t last_hash = 0;
     for (int s = 0; s < static_cast<int>(slot_key.size()); ++s) {
         const int valid = static_cast<int>(slot_key[s] & 0xffffffffu);
         const int32_t page = static_cast<int32_t>(slot_key[s] >> 32);
         // a partial page always gets a segment key of its own signature hash so that
         // two partial pages never land in one segment
         uint64_t h = slot_hash[s];
-        auto& cand = seg_by_hash[h];
         int seg = -1;
-        for (int c : cand) {
-            if (same_sig(seg_rep[c], s) && !(valid < page_size && segs[c].partial_tokens > 0)) {
-                seg = c;
-                break;
+        // consecutive pages of a box nearly always share their signature: try the segment of the
+        // previous slot before the hash map
+        if (last_seg >= 0 && h == last_hash && same_sig(seg_rep[last_seg], s) &&
+            !(valid < page_size && segs[last_seg].partial_tokens > 0))
+            seg = last_seg;
+        if (seg < 0) {
+            for (int c : seg_by_hash[h]) {
+                if (same_sig(seg_rep[c], s) && !(valid < page_size && segs[c].partial_tokens > 0)) {
+                    seg = c;
+                    break;
+                }
             }
         }
         if (seg < 0) {
             seg = static_cast<int>(segs.size());
             segs.emplace_back();
             seg_rep.push_back(s);
-            cand.push_back(seg);
+            seg_by_hash[h].push_back(seg);
             for (int l = slot_head[s]; l >= 0; l = link_next[l]) {
                 const auto& q = fused[link_box[l]].queries;
                 segs[seg].queries.insert(segs[seg].queries.end(), q.begin(), q.end());
             }
         }
+        last_seg = seg;
+        last_hash = h;
         Segment& sg = segs[seg];
         if (valid < page_size) {
             sg.partial_tokens = valid;      // appended after the loop, so that it is last
