@@ -83,9 +83,10 @@ class DeviceWork:
         lib.pat_work_get_header(handle, C.byref(self.header))
         words = C.c_size_t()
         ptr = lib.pat_work_blob(handle, C.byref(words))
-        host = torch.from_numpy(np.ctypeslib.as_array(ptr, shape=(words.value,)).copy())
-        if device.type == "cuda":
-            host = host.pin_memory()
+        # one copy: native blob -> (pinned) host tensor
+        host = torch.empty(words.value, dtype=torch.int32, pin_memory=device.type == "cuda")
+        if words.value:
+            C.memmove(host.data_ptr(), ptr, words.value * 4)
         self._host = host                       # kept alive until the async copy is done
         self.blob = host.to(device, non_blocking=True)
         self.device = device

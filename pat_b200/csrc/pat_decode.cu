@@ -38,18 +38,17 @@ EncodeFn get_encode_fn() {
 // View of a paged cache [pages, page_size, kv_heads, D] as a 4-D tensor
 // (D, kv_heads, page_size, pages) with a [64, 1, 16, 1] box and 128-byte swizzle.
 int make_cache_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int head_dim, int kv_heads,
-                   int page_size, int64_t pages, int64_t head_stride, int64_t row_stride, int64_t page_stride,
-                   bool wide = false) {
+                   int page_size, int64_t pages, int64_t head_stride, int64_t row_stride, int64_t page_stride) {
     EncodeFn enc = get_encode_fn();
     if (!enc) return PAT_ERR_CUDA;
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(kv_heads),
                                 static_cast<cuuint64_t>(page_size), static_cast<cuuint64_t>(pages)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_stride) * 2, static_cast<cuuint64_t>(row_stride) * 2,
                                    static_cast<cuuint64_t>(page_stride) * 2};
-    const cuuint32_t box[4] = {wide ? static_cast<cuuint32_t>(head_dim) : 64u, 1, 16, 1};
+    const cuuint32_t box[4] = {64u, 1, 16, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult rc = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            wide ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return rc == CUDA_SUCCESS ? PAT_OK : PAT_ERR_CUDA;
 }
@@ -89,7 +88,6 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     p.scale = a.softmax_scale;
     p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
     p.status = a.status_word;
-    p.debug = a.flags >> 8;
 
     int launches = 0;
     const bool streaming = a.work.num_stream_items > 0 && !(a.flags & PAT_SKIP_STREAM);

@@ -43,6 +43,7 @@ constexpr int kTcSoftmaxWarps = 8;
 constexpr int kTcThreads = (kTcSoftmaxWarps + 3) * 32;
 constexpr int kTcTmemCols = 512;
 constexpr float kTcLazyLog2 = 8.0f;
+constexpr int kTcPolyEvery = 4;             // every 4th pair of scores gets its exponential from the FMA pipe (0 = none)
 
 template <int D> struct TcSmem {
     static constexpr int kBoxes = D / 64;
@@ -217,10 +218,19 @@ template <int N> __device__ __forceinline__ void tmem_st_f(uint32_t taddr, const
     else tmem_st32(taddr, reinterpret_cast<const uint32_t (&)[32]>(v));
 }
 
-__device__ __forceinline__ long long tc_clock() {
-    long long c;
-    asm volatile("mov.u64 %0, %clock64;" : "=l"(c));
-    return c;
+// 2^x for x <= about 10 without the special-function unit: x = n + f with n = round(x) and
+// f in [-0.5, 0.5]; 2^f by a degree-4 polynomial (relative error 5e-5, far below the 16-bit
+// rounding of P); 2^n by adding n to the exponent field.  Inputs below -126 give 2^-126.
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -126.f);
+    const float magic = 12582912.f;             // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+    const float t = x + magic;
+    const float f = x - (t - magic);
+    float p = fmaf(f, 9.6181291e-3f, 5.5504109e-2f);
+    p = fmaf(p, f, 2.4022651e-1f);
+    p = fmaf(p, f, 6.9314718e-1f);
+    p = fmaf(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
 struct DenseTcParams {
@@ -264,7 +274,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
 
     const int item_lo = __ldg(dp.cta_begin + blockIdx.x), item_hi = __ldg(dp.cta_begin + blockIdx.x + 1);
     if (item_lo >= item_hi) return;     // a CTA without work (uniform)
-    if ((p.debug & 128) && (blockIdx.x & 1)) return;    // experiment: odd CTAs idle
 
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
@@ -283,9 +292,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o_col = R * kTcTile;    // O behind the S ring
     const int tiles_per_page = p.page_size >> 4;
-    // experiment: CTA 0 records clock64 time stamps of its first 96 tiles behind the status word
-    long long* trace = (p.debug & 64) && blockIdx.x == 0 && p.status ? reinterpret_cast<long long*>(p.status + 16) : nullptr;
-    auto stamp = [&](int tile, int what) { if (trace && tile < 96) trace[tile * 16 + what] = tc_clock(); };
 
     if (warp == kSW || warp == kSW + 2) {
         // ---- TMA producers: one warp streams K, one streams V ---------------------------------
@@ -306,7 +312,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             for (int j = 0; j < n_tiles; ++j, ++t) {
                 if (t >= R) ok = mbar_wait(empty + 8 * s, ph);
                 if (!ok) break;
-                if (is_k && lane == 0) stamp(t, 0);
                 constexpr int kSub = kTcTile / 16;
                 const int subs = min(kSub, n_sub - j * kSub);
                 if (lane == 0) mbar_expect_tx(full + 8 * s, subs * (L::kBoxes * 2048));
@@ -371,7 +376,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (ok) ok = mbar_wait(bar_full_k + 8 * slot, phase);
             ok = __all_sync(kFullMask, ok);
             tc_fence_after();
-            if (!(p.debug & 4)) {
+            {
                 uint32_t q_w = q_lo, k_w = k_lo0 + slot * kSlotStep, acc = 0;
 #pragma unroll
                 for (int ks = 0; ks < kSteps; ++ks) {
@@ -396,7 +401,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const bool qk = have_a && !a_new_item;
             const int sa = slot_add(s, 2);
             const uint32_t pha = sa < s ? ph ^ 1 : ph;
-            if (lane == 0) stamp(g, 7);
             if (qk && ok) ok = mbar_wait(bar_full_k + 8 * sa, pha);
             if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
             if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(g) is in TMEM (over S(g))
@@ -404,19 +408,17 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 ok = mbar_wait(bar_ofree, (pv_items - 1) & 1);     // the softmax warps have read the previous item's O
             ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
             tc_fence_after();
-            if (lane == 0) stamp(g, 1);
             // slot sa held tile g - 1, whose P V was issued in the previous iteration; MMAs execute in
             // issue order, so S(g + 2) may overwrite it now
             {
-                const bool do_qk = qk && !(p.debug & 4), pv = !(p.debug & 8);
                 uint32_t q_w = q_lo, k_w = k_lo0 + sa * kSlotStep, v_w = v_lo0 + s * kSlotStep;
                 uint32_t p_col = tmem_base + s * kTcTile;
                 const uint32_t s_col = tmem_base + sa * kTcTile, o_col = tmem_base + tmem_o_col;
                 uint32_t acc_s = 0, acc_o = pv_j > 0 ? 1u : 0u;
 #pragma unroll
                 for (int i = 0; i < kTcTile / 16; ++i) {
-                    if (do_qk && i < kSteps && elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
-                    if (pv && elect_one()) tc_mma_ts(o_col, p_col, desc(v_w), idesc_pv, acc_o);
+                    if (qk && i < kSteps && elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
+                    if (elect_one()) tc_mma_ts(o_col, p_col, desc(v_w), idesc_pv, acc_o);
                     // k-step i + 1 of a K-major operand of 128 rows: 32 B on, or into the next 64-element box
                     const uint32_t step = (i & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
                     q_w += step;
@@ -427,7 +429,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                     acc_o = 1;
                 }
             }
-            if (lane == 0) stamp(g, 6);
             if (qk) {
                 if (elect_one()) tc_commit(bar_s + 8 * sa);
                 if (elect_one()) tc_commit(bar_empty_k + 8 * sa);
@@ -435,7 +436,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             }
             if (elect_one()) tc_commit(bar_o + 8 * s);
             if (elect_one()) tc_commit(bar_empty_v + 8 * s);
-            if (lane == 0) stamp(g, 2);
             if (++pv_j == pv_n) { ++pv_item; ++pv_items; pv_j = 0; pv_n = tiles_of(pv_item); }
             if (a_new_item) qk_alone(sa, pha);  // waits for the next item's Q, which the softmax warps
                                                 // write once they have seen the last S of this item
@@ -515,7 +515,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const uint4* q_next = item + 1 < item_hi ? q_addr(item + 1) : nullptr;
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j, ++t) {
-            if (tid == 0) stamp(t, 3);
             if (j == n_tiles - 1 && item + 1 < item_hi) {
                 // Last tile of the item.  Once its S has completed, so has every Q K^T of the item,
                 // and the Q rows of the next item can take their place: the MMA warp then requests
@@ -531,21 +530,15 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
                 tc_fence_after();
             }
-            if (tid == 0) stamp(t, 4);
             constexpr int CH = kTcTile / 2;     // token columns per thread
             float sc[CH];
-            if (!(p.debug & 2)) tmem_ld_f<CH>(lane_addr + s * kTcTile + half * CH, sc);
-            else {
-#pragma unroll
-                for (int i = 0; i < CH; ++i) sc[i] = 0.f;
-            }
+            tmem_ld_f<CH>(lane_addr + s * kTcTile + half * CH, sc);
             const int valid = min(kTcTile, kv_len - j * kTcTile);
             if (valid < kTcTile) {
 #pragma unroll
                 for (int i = 0; i < CH; ++i)
                     if (half * CH + i >= valid) sc[i] = -INFINITY;
             }
-            if (tid == 0) stamp(t, 8);
             float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
 #pragma unroll
             for (int i = 4; i < CH; i += 4) {
@@ -556,8 +549,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             xbuf[half * 128 + r] = fmaxf(mx0, mx1);
             pair_sync();
             const float mx = fmaxf(fmaxf(mx0, mx1), xbuf[(half ^ 1) * 128 + r]);
-            if (tid == 0) stamp(t, 9);
-
             const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
             if (j > 0 && __any_sync(kFullMask, raise)) {
                 ensure_o(t);            // O may only be touched once every earlier P V has completed
@@ -573,25 +564,22 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const float off = m_used * c;
             float sum0 = 0.f, sum1 = 0.f;
             uint32_t packed[CH / 2];
-            if (!(p.debug & 1)) {
+            // One exponential per score is what bounds this loop (16 per clock and SM on the
+            // special-function unit), so every kTcPolyEvery-th pair is computed on the FMA pipe
+            // instead (exp2_poly); P is rounded to 16 bits anyway.
 #pragma unroll
-                for (int i = 0; i < CH / 2; ++i) {
-                    const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
-                    const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
-                    sum0 += p0;
-                    sum1 += p1;
-                    packed[i] = Elt<T>::pack(p0, p1);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < CH / 2; ++i) packed[i] = 0x3c003c00u + static_cast<uint32_t>(sc[i] > 1e30f);
-                sum0 = static_cast<float>(CH);
+            for (int i = 0; i < CH / 2; ++i) {
+                const float x0 = fmaf(sc[2 * i], c, -off), x1 = fmaf(sc[2 * i + 1], c, -off);
+                const bool poly = kTcPolyEvery > 0 && (i % (kTcPolyEvery > 0 ? kTcPolyEvery : 1)) == 0;
+                const float p0 = poly ? exp2_poly(x0) : fast_exp2(x0);
+                const float p1 = poly ? exp2_poly(x1) : fast_exp2(x1);
+                sum0 += p0;
+                sum1 += p1;
+                packed[i] = Elt<T>::pack(p0, p1);
             }
             l += sum0 + sum1;
-            if (tid == 0) stamp(t, 10);
             // P over the S columns this row has consumed: CH / 2 packed columns per half
-            if (!(p.debug & 16)) tmem_st32(lane_addr + s * kTcTile + half * (CH / 2), packed);
-            if (tid == 0) stamp(t, 11);
+            tmem_st32(lane_addr + s * kTcTile + half * (CH / 2), packed);
             if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
@@ -612,7 +600,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             ensure_o(t - R + 1);
             tc_fence_before();
             mbar_arrive(bar_p + 8 * s);
-            if (tid == 0) stamp(t, 5);
             if (++s == R) { s = 0; ph ^= 1; }
         }
 
@@ -626,9 +613,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             pair_sync();
             const float l_row = l + xbuf[(half ^ 1) * 128 + r];
             pair_sync();                        // both have read before the buffer is reused
-            if (tid == 0) stamp(t - 1, 12);
             ensure_o(t);
-            if (tid == 0) stamp(t - 1, 13);
             const bool store = ok && r < rows_valid;
             size_t slot = 0;
             if (r < rows_valid) {
@@ -640,7 +625,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             tmem_ld_f<OC>(tmem_o, ov);
             tc_fence_before();
             mbar_arrive(bar_ofree);             // O may be overwritten by the next item's first P V
-            if (tid == 0) stamp(t - 1, 14);
             if (store) {
                 // 32 bytes per store: the rows of a warp lie D floats apart, so every store instruction
                 // touches 32 lines whatever its width, and the wide form halves their number
@@ -654,7 +638,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                                  : "memory");
                 if (half == 0) p.part_lse[slot] = m_used * p.scale + logf(l_row);
             }
-            if (tid == 0) stamp(t - 1, 15);
         }
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);

@@ -41,7 +41,6 @@ struct AttnParams {
     float scale;          // softmax scale
     float scale_log2;     // scale * log2(e)
     int32_t* status;      // optional
-    int debug;            // experiment switches (flags >> 8); 0 in normal use
 };
 
 constexpr int kStreamWarps = 3;
