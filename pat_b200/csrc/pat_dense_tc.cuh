@@ -43,7 +43,6 @@ constexpr int kTcSoftmaxWarps = 8;
 constexpr int kTcThreads = (kTcSoftmaxWarps + 3) * 32;
 constexpr int kTcTmemCols = 512;
 constexpr float kTcLazyLog2 = 8.0f;
-constexpr int kTcPolyEvery = 4;             // every 4th pair of scores gets its exponential from the FMA pipe (0 = none)
 
 template <int D> struct TcSmem {
     static constexpr int kBoxes = D / 64;
@@ -216,21 +215,6 @@ template <int N> __device__ __forceinline__ void tmem_ld_f(uint32_t taddr, float
 template <int N> __device__ __forceinline__ void tmem_st_f(uint32_t taddr, const float (&v)[N]) {
     if constexpr (N == 64) tmem_st64(taddr, v);
     else tmem_st32(taddr, reinterpret_cast<const uint32_t (&)[32]>(v));
-}
-
-// 2^x for x <= about 10 without the special-function unit: x = n + f with n = round(x) and
-// f in [-0.5, 0.5]; 2^f by a degree-4 polynomial (relative error 5e-5, far below the 16-bit
-// rounding of P); 2^n by adding n to the exponent field.  Inputs below -126 give 2^-126.
-__device__ __forceinline__ float exp2_poly(float x) {
-    x = fmaxf(x, -126.f);
-    const float magic = 12582912.f;             // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
-    const float t = x + magic;
-    const float f = x - (t - magic);
-    float p = fmaf(f, 9.6181291e-3f, 5.5504109e-2f);
-    p = fmaf(p, f, 2.4022651e-1f);
-    p = fmaf(p, f, 6.9314718e-1f);
-    p = fmaf(p, f, 1.0f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
 struct DenseTcParams {
@@ -564,15 +548,13 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const float off = m_used * c;
             float sum0 = 0.f, sum1 = 0.f;
             uint32_t packed[CH / 2];
-            // One exponential per score is what bounds this loop (16 per clock and SM on the
-            // special-function unit), so every kTcPolyEvery-th pair is computed on the FMA pipe
-            // instead (exp2_poly); P is rounded to 16 bits anyway.
+            // One exponential per score on the special-function unit (16 per clock and SM) and about
+            // as many cycles of FMA-pipe work (scale, sum, 16-bit packing) per tile: moving a share of
+            // the exponentials to the FMA pipe as a polynomial made the tile slower, not faster.
 #pragma unroll
             for (int i = 0; i < CH / 2; ++i) {
-                const float x0 = fmaf(sc[2 * i], c, -off), x1 = fmaf(sc[2 * i + 1], c, -off);
-                const bool poly = kTcPolyEvery > 0 && (i % (kTcPolyEvery > 0 ? kTcPolyEvery : 1)) == 0;
-                const float p0 = poly ? exp2_poly(x0) : fast_exp2(x0);
-                const float p1 = poly ? exp2_poly(x1) : fast_exp2(x1);
+                const float p0 = fast_exp2(fmaf(sc[2 * i], c, -off));
+                const float p1 = fast_exp2(fmaf(sc[2 * i + 1], c, -off));
                 sum0 += p0;
                 sum1 += p1;
                 packed[i] = Elt<T>::pack(p0, p1);
