@@ -305,18 +305,18 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / (static_cast<int64_t>(kv_heads) * row_lanes));
         int64_t share_limit = max_shares;
         if (opt.dense_tile_ns > 0 && header_.stream_tokens > 0) {
-            // Both kernels run at the same time.  When the call is dominated by the streaming
-            // kernel's HBM traffic (about kStreamPsPerTokenHead per token and KV head: 512 bytes at
-            // 6.5 TB/s), the dense kernel - bound by the tensor and special-function units of the
-            // SMs it holds, not by memory - gets only the CTAs it needs to finish a little before
-            // the streaming kernel does; the streaming kernel fills the other SMs.  Short calls are
-            // bound by latencies this estimate knows nothing about: there the dense kernel is cut
-            // for every SM.
-            constexpr double kStreamPsPerTokenHead = 79.0, kWindowShare = 0.85, kMinWindowNs = 150e3;
-            constexpr double kItemNs = 8000.0, kFixedNs = 25000.0;   // per dense item (pipeline fill and drain), per launch
+            // Both kernels run at the same time.  The streaming kernel is bound by HBM (about
+            // kStreamPsPerTokenHead per token and KV head: 512 bytes at 6.5 TB/s) and keeps most of
+            // its speed on fewer SMs; the dense kernel is bound by the tensor and special-function
+            // units of the SMs it holds, not by memory.  So the dense kernel gets only the CTAs it
+            // needs to finish within kWindowShare of the time the step's HBM traffic takes, and the
+            // streaming kernel fills the other SMs.  The dense time is estimated as a fixed part
+            // plus (tiles x dense_tile_ns + items x kItemNs) / CTAs, calibrated on a B200.
+            constexpr double kStreamPsPerTokenHead = 79.0, kWindowShare = 0.8;
+            constexpr double kItemNs = 6000.0, kFixedNs = 8000.0;   // per dense item (fill and drain), per launch
             const double window_ns = static_cast<double>(header_.stream_tokens + header_.dense_unique_tokens) *
                                      kv_heads * kStreamPsPerTokenHead * 1e-3;
-            if (window_ns >= kMinWindowNs) {
+            {
                 const int64_t group = static_cast<int64_t>(kv_heads) * row_lanes;      // CTAs per share
                 int64_t chunk_sum = 0;
                 for (const DenseSeg& d : dsegs) chunk_sum += d.chunks;
