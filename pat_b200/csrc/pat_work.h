@@ -48,7 +48,7 @@ struct WorkOptions {
     int chunk_tokens_min = 256;
     int chunk_tokens_max = 2048;
     int dense_piece_tokens_min = 512;  // a dense share is not cut (much) below this many tokens
-    int items_per_sm = 8;              // target number of streaming items per SM (all KV heads)
+    int items_per_sm = 4;              // target number of streaming items per SM (all KV heads)
     // Estimated time of one 128-token tile of the dense kernel.  When a work list has streaming
     // work too, the dense kernel runs beside the streaming kernel and gets only as many CTAs as
     // it needs to finish within the time the streaming kernel needs for its HBM traffic.
