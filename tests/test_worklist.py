@@ -214,3 +214,35 @@ def test_bad_plan_is_rejected(native_lib):
     from pat_b200 import _native as N
     with pytest.raises(AssertionError):
         W.build_work(([[[7]]], [[[0]]], [[1]], [[16]]), 4, 1, 1, 16)   # query id 7 >= batch 4
+
+
+def test_dense_share_of_the_sms(native_lib):
+    """When a plan has streaming work too, the dense kernel is cut for a share of the SMs
+    sized from `dense_tile_ns`; without the estimate (< 0) or without streaming work it is
+    cut for all of them.  Whatever the cut, the same tokens are covered."""
+    w = make_config(4)
+    t = PrefixTree(w.page_size)
+    t.build_radix_tree(list(w.seq_lens), [list(r) for r in w.block_tables])
+    for hk in (w.num_kv_heads, 1):                       # one GPU, and one rank of eight
+        ki = t.pack_schedule(None, w.group, hk)
+        lists = _plan_lists(ki)
+        counts = {}
+        for tile_ns in (-1, 800, 1600, 3200):
+            header, blob = W.build_work(lists, w.batch, w.group, hk, w.page_size, dense_tile_ns=tile_ns)
+            ctas = W.dense_ctas(header, blob)
+            items = W.items_of(header, blob)[header.num_stream_items:]
+            assert items[:, 3].sum() == header.dense_tokens * hk
+            assert header.num_dense_ctas == len(ctas) <= 148
+            assert len(ctas) % hk == 0
+            counts[tile_ns] = len(ctas)
+        assert counts[800] <= counts[1600] <= counts[3200] <= counts[-1]
+        assert counts[1600] < counts[-1]
+        assert counts[-1] > 148 - 2 * hk * 2             # all SMs, up to one group of CTAs
+    # dense work only (every request shares everything): no streaming kernel to run beside
+    lens = [4096] * 64
+    tables = [list(range(256))] * 64
+    t2 = PrefixTree(16)
+    t2.build_radix_tree(lens, tables)
+    ki = t2.pack_schedule(None, 4, 8)
+    header, blob = W.build_work(_plan_lists(ki), 64, 4, 8, 16)
+    assert header.num_stream_items == 0 and header.num_dense_ctas > 100
