@@ -331,6 +331,15 @@ def main():
     k_ms["merge_kernel"] = timed(capture(lambda: step(1 | 2)), reps)
     step()   # leave `out` complete
 
+    # the step right before attention in a serving loop: append one new token per request to the
+    # paged cache (rewrites every request's last token with the values it already has)
+    from pat_b200.cache_ops import reshape_and_cache_flash
+    last = torch.tensor([w.block_tables[b][(w.seq_lens[b] - 1) // page] * page + (w.seq_lens[b] - 1) % page
+                         for b in range(B)], dtype=torch.int64, device=dev)
+    new_k = k_cache.view(-1, hk, D)[last].clone()
+    new_v = v_cache.view(-1, hk, D)[last].clone()
+    append_ms = timed(capture(lambda: reshape_and_cache_flash(new_k, new_v, k_cache, v_cache, last)), reps)
+
     # end to end: host queries + work list in, output back, every step
     blob_host = work._host
     def e2e_step():
@@ -403,6 +412,8 @@ def main():
                  "entries": hdr.num_entries, "segments": hdr.num_segments,
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
         "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},
+        "append_kv": {"us": append_ms * 1e3, "tokens": B, "bytes": int(2 * 2 * B * hk * D * elt),
+                      "note": "KV-cache append of one token per request (separate launch, not part of value)"},
     }
 
     if n == 1 and not args.no_cpu_baseline:

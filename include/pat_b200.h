@@ -220,6 +220,32 @@ int pat_b200_last_launch_count(void);
 #define PAT_B200_STATIC_SCRATCH_BYTES (32u << 20)
 int pat_b200_decode_static_scratch(const pat_decode_args* args, void* stream);
 
+/* ------------------------------------------------------------------------- *
+ * KV-cache append: the step right before decode attention.
+ * Replaces vLLM's reshape_and_cache_flash as called from the reference's serving backend
+ * (plugin/vllm/attention/backends/prefix_attn.py:828-837): the K and V rows of the new tokens
+ * are written into the paged caches at slot_mapping[token] = page * page_size + row.  A
+ * negative slot (vLLM's padding id) is skipped, and so is a slot beyond the cache.
+ * 16-bit caches only (kv_cache_dtype "auto"); rows are copied bit for bit.
+ * ------------------------------------------------------------------------- */
+typedef struct pat_append_args {
+    const void* key;               /* [num_tokens, num_kv_heads, head_dim] */
+    const void* value;
+    void* k_cache;                 /* [num_pages, page_size, num_kv_heads, head_dim] */
+    void* v_cache;
+    const int64_t* slot_mapping;   /* device, [num_tokens] */
+    /* strides in elements (multiples of 8), last dimension contiguous, 16-byte aligned bases */
+    int64_t key_token_stride, key_head_stride, value_token_stride, value_head_stride;
+    int64_t k_page_stride, k_row_stride, k_head_stride;
+    int64_t v_page_stride, v_row_stride, v_head_stride;
+    int64_t num_pages;
+    int32_t num_tokens, num_kv_heads, head_dim, page_size;
+    int32_t dtype;                 /* PAT_DTYPE_* */
+    int32_t reserved;
+} pat_append_args;
+
+int pat_b200_append_kv(const pat_append_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,18 @@ class DecodeArgs(C.Structure):
                 ("status_word", C.c_void_p)]
 
 
+class AppendArgs(C.Structure):
+    _fields_ = [("key", C.c_void_p), ("value", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("slot_mapping", C.c_void_p),
+                ("key_token_stride", C.c_int64), ("key_head_stride", C.c_int64),
+                ("value_token_stride", C.c_int64), ("value_head_stride", C.c_int64),
+                ("k_page_stride", C.c_int64), ("k_row_stride", C.c_int64), ("k_head_stride", C.c_int64),
+                ("v_page_stride", C.c_int64), ("v_row_stride", C.c_int64), ("v_head_stride", C.c_int64),
+                ("num_pages", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("page_size", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
 # name -> (restype, argtypes); also the list of symbols the header declares.
 SIGNATURES = {
     "pat_b200_strerror": (C.c_char_p, [C.c_int]),
@@ -90,6 +102,7 @@ SIGNATURES = {
     "pat_b200_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "pat_b200_last_launch_count": (C.c_int, []),
     "pat_b200_decode_static_scratch": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "pat_b200_append_kv": (C.c_int, [C.POINTER(AppendArgs), C.c_void_p]),
 }
 STATIC_SCRATCH_BYTES = 32 << 20
 
