@@ -1,5 +1,5 @@
-"""Freezes golden vectors from the reference itself.  Run in a container that
-has the read-only reference checkout (default ``/root/reference``):
+"""Freezes golden vectors from the reference itself.  Run where the read-only reference
+checkout is present (its location: environment variable ``PAT_REFERENCE_ROOT``):
 
     python tests/golden/make_golden.py
 

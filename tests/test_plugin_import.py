@@ -18,7 +18,9 @@ import types
 
 import pytest
 
-PLUGIN = "/root/reference/plugin/vllm/attention/backends/prefix_attn.py"
+from oracle.ref_loader import REFERENCE_ROOT
+
+PLUGIN = os.path.join(REFERENCE_ROOT, "plugin", "vllm", "attention", "backends", "prefix_attn.py")
 pytestmark = pytest.mark.skipif(not os.path.isfile(PLUGIN), reason="reference checkout not present")
 
 
