@@ -17,10 +17,14 @@
 //            of 16 tokens x 64 elements, 128-byte swizzle - the layout the UMMA shared-memory
 //            descriptors describe).  A K tile is released as soon as its S = Q K^T has
 //            completed, a V tile when its P V has.
-//   warp 9:  one thread issues every MMA: S(t) = Q K_t^T (M128 N128 K16 x D/16, both operands
-//            from shared memory) two tiles ahead of the softmax, and O += P(t) V_t (M128 N=D
-//            K16 x 8, A = P from TMEM, B = V from shared memory); completion is signalled with
-//            tcgen05.commit on mbarriers.
+//   warp 9:  issues every MMA (the whole warp runs the loop, one elected lane issues):
+//            S(g + 2) = Q K^T (M128 N128 K16 x D/16, both operands from shared memory) two tiles
+//            ahead of the softmax, interleaved with O += P(g) V(g) (M128 N=D K16 x 8, A = P from
+//            TMEM, B = V from shared memory); completion is signalled with tcgen05.commit on
+//            mbarriers.  The items of a CTA form one stream of tiles: the Q rows of the next item
+//            are written into shared memory during the last tile of the current one, so its
+//            first S tiles are requested before the current item has finished, and an "O free"
+//            barrier keeps its first P V from overwriting an accumulator that is still being read.
 //
 // Two measured facts shape the pipeline.  A tcgen05.commit needs of the order of a microsecond
 // to reach its mbarrier, so S lives in a ring of three 128-column TMEM buffers (3 x 128 + D
@@ -155,22 +159,6 @@ __device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[64]) 
 }
 
 // ---- UMMA descriptors -------------------------------------------------------------
-// Shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4),
-// descriptor version 1, 128-byte swizzle (layout type 2).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu) |
-           (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16) |
-           (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
-// K-major operand (rows of 128 B = 64 elements, groups of 8 rows 1024 B apart): the leading
-// offset is unused by the swizzled K-major layouts and set to 16 B.
-__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr) { return umma_desc(smem_addr, 16, 1024); }
-// MN-major operand: 64 elements along MN per 128-B row, next 64 along MN `mn_stride` bytes on,
-// groups of 8 K-rows 1024 B apart.
-__device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t smem_addr, uint32_t mn_stride) {
-    return umma_desc(smem_addr, mn_stride, 1024);
-}
 // Instruction descriptor of kind::f16: fp32 accumulate, A/B format (0 = f16, 1 = bf16),
 // A K-major, B K-major or MN-major, N >> 3 at bit 17, M >> 4 at bit 24.
 template <typename T> __device__ __forceinline__ uint32_t umma_idesc(int m, int n, bool b_mn_major) {
@@ -183,7 +171,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// 32 consecutive fp32 columns / 16 consecutive 32-bit columns of this thread's TMEM lane
+// 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
     asm volatile(
@@ -197,16 +185,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // N consecutive fp32 columns (N = 32 or 64)
 template <int N> __device__ __forceinline__ void tmem_ld_f(uint32_t taddr, float (&v)[N]) {
@@ -328,6 +306,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const uint32_t idesc_pv = umma_idesc<T>(128, D, true);
         constexpr int kSteps = D / 16;          // k-steps of a QK product
         static_assert(kTcTile == 128, "the k-step arithmetic below assumes K tiles of 128 rows, like Q");
+        // Shared-memory matrix descriptor (64 bits): start address >> 4 in bits 0-13, leading byte
+        // offset >> 4 in 16-29, stride byte offset >> 4 in 32-45, descriptor version 1 in 46-47,
+        // layout type 2 (128-byte swizzle) in 61-63.  K-major operands (Q, K): rows of 128 B = 64
+        // elements, groups of 8 rows 1024 B apart (stride offset), leading offset unused.  MN-major
+        // operand (V): 64 elements along N per 128-B row, the next 64 one tile column on (leading
+        // offset), groups of 8 K-rows 1024 B apart.
         constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024 B, version 1, 128-B swizzle
         constexpr uint32_t kSlotStep = static_cast<uint32_t>(L::kKBytes) >> 4;
         const uint32_t q_lo = ((sQ >> 4) & 0x3fffu) | (1u << 16);            // K-major: leading offset unused (16 B)
