@@ -98,6 +98,51 @@ def test_random_batches(dtype, hq, hk, d, page, seed, native_lib):
     _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
 
 
+def _random_forest(seed, page=16, cap=400):
+    """Requests as root-to-leaf paths of random trees whose segments are 1..44 pages long (ragged
+    against the kernels' 128-token tiles), tails of 1..299 tokens, random physical placement."""
+    rng = np.random.default_rng(1000 + seed)
+    next_page = [0]
+
+    def alloc(n):
+        first = next_page[0]
+        next_page[0] += n
+        return list(range(first, first + n))
+
+    reqs = []
+
+    def grow(prefix, depth):
+        if depth == 0 or (depth < 3 and rng.random() < 0.15):
+            for _ in range(int(rng.integers(1, 5))):
+                tail = int(rng.integers(1, 300))
+                reqs.append((prefix + alloc(-(-tail // page)), len(prefix) * page + tail))
+            return
+        for _ in range(int(rng.integers(2, 6))):
+            grow(prefix + alloc(int(rng.integers(1, 45))), depth - 1)
+
+    for _ in range(int(rng.integers(1, 4))):
+        grow(alloc(int(rng.integers(1, 60))), int(rng.integers(1, 4)))
+    reqs = reqs[:cap]
+    order = rng.permutation(next_page[0])
+    tables = [[int(order[p]) for p in pages] for pages, _ in reqs]
+    return [l for _, l in reqs], tables, next_page[0]
+
+
+@pytest.mark.parametrize("seed", [2, 4, 5, 10])
+@pytest.mark.parametrize("dtype,hq,hk,d", [(torch.bfloat16, 32, 4, 128), (torch.float16, 16, 2, 64)])
+def test_random_forests_with_ragged_segments(seed, dtype, hq, hk, d, native_lib):
+    """Many dense items per persistent CTA, with 1, 2, 3+ tiles and partial last tiles: the tile
+    stream of the tcgen05 kernel crosses item boundaries all the time."""
+    lens, tables, pages = _random_forest(seed)
+    q, k, v = _values(pages, 16, hq, hk, d, len(lens), dtype, seed)
+    scale = 1.0 / math.sqrt(d)
+    out, lse, tree = _run_tree(q, k, v, lens, tables, 16, hq // hk, hk, scale)
+    hdr = tree.kernel_info.device_work(torch.device(DEV)).header
+    assert hdr.num_dense_items > hdr.num_dense_ctas > 0
+    ref_o, ref_l = O.paged_decode_attention(q, k, v, lens, tables, scale)
+    _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
+
+
 @pytest.mark.parametrize("cfg", [0, 1, 2])
 def test_benchmark_configs_full(cfg, native_lib):
     w = make_config(cfg)
