@@ -12,7 +12,7 @@ import pat_b200 as _impl
 from pat_b200 import *  # noqa: F401,F403
 from pat_b200 import __all__  # noqa: F401
 
-for _name in ("_prefix_attn", "data_class", "prefix_tree", "block_scheduler", "utils", "async_tree"):
+for _name in ("_prefix_attn", "data_class", "prefix_tree", "block_scheduler", "utils", "async_tree", "cache_ops"):
     _mod = _importlib.import_module(f"pat_b200.{_name}")
     _sys.modules[f"{__name__}.{_name}"] = _mod
     globals()[_name] = _mod
