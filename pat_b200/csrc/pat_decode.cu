@@ -104,13 +104,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     const bool overlap = streaming && dense_tc && !(a.flags & PAT_NO_OVERLAP);
     if (dense_tc) {
         // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
-        static bool configured[kMaxDevices] = {};
+        static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
         auto kern = dense_tc_kernel<T, D>;
         constexpr int smem = TcSmem<D>::kRequest;
-        if (!configured[dev]) {
+        if (!configured[dev].load(std::memory_order_acquire)) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
                 return PAT_ERR_CUDA;
-            configured[dev] = true;
+            configured[dev].store(true, std::memory_order_release);
         }
         AttnParams pd = p;
         pd.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
@@ -122,13 +122,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         ++launches;
     }
     if (streaming) {
-        static bool configured[kMaxDevices] = {};
+        static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
         auto kern = stream_kernel<T, D>;
         constexpr int smem = stream_smem_bytes<D>();
-        if (!configured[dev]) {
+        if (!configured[dev].load(std::memory_order_acquire)) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
                 return PAT_ERR_CUDA;
-            configured[dev] = true;
+            configured[dev].store(true, std::memory_order_release);
         }
         p.items = a.work_blob + a.work.items_off;
         p.num_items = a.work.num_stream_items;
@@ -150,13 +150,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     if (dense && !dense_tc) {
         // the same items on the legacy mma.sync path (kept for comparison): one CTA per
         // (item, 128-row half)
-        static bool configured[kMaxDevices] = {};
+        static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
         auto kern = dense_kernel<T, D>;
         constexpr int smem = dense_smem_bytes<D>();
-        if (!configured[dev]) {
+        if (!configured[dev].load(std::memory_order_acquire)) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
                 return PAT_ERR_CUDA;
-            configured[dev] = true;
+            configured[dev].store(true, std::memory_order_release);
         }
         p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
         p.num_items = a.work.num_dense_items;
