@@ -29,7 +29,8 @@ typedef enum pat_status {
     PAT_ERR_WORKSPACE = -12,         /* workspace missing, too small or not 32-byte aligned */
     PAT_ERR_CUDA = -13,              /* a CUDA runtime or driver call failed */
     PAT_ERR_NO_DEVICE_CODE = -14,    /* the GPU is not an sm_100 part */
-    PAT_ERR_TOO_LARGE = -15          /* size beyond a fixed limit */
+    PAT_ERR_TOO_LARGE = -15,         /* size beyond a fixed limit */
+    PAT_ERR_NO_MEMORY = -16          /* host allocation failed (no C++ exception leaves the library) */
 } pat_status;
 
 const char* pat_b200_strerror(int status);

@@ -74,6 +74,7 @@ const char* pat_b200_strerror(int status) {
         case PAT_ERR_CUDA: return "a CUDA call failed";
         case PAT_ERR_NO_DEVICE_CODE: return "this library only carries sm_100a device code";
         case PAT_ERR_TOO_LARGE: return "size exceeds a fixed limit";
+        case PAT_ERR_NO_MEMORY: return "out of host memory";
         default: return "unknown status";
     }
 }
@@ -88,19 +89,25 @@ void pat_tree_destroy(pat_tree* t) { delete t; }
 int pat_tree_build(pat_tree* t, const int32_t* seq_lens, const int32_t* block_table, int num_seqs,
                    int row_stride) {
     if (!t) return PAT_ERR_BAD_ARGUMENT;
-    return t->tree.build_padded(seq_lens, block_table, num_seqs, row_stride);
+    try {
+        return t->tree.build_padded(seq_lens, block_table, num_seqs, row_stride);
+    } catch (...) { return PAT_ERR_NO_MEMORY; }
 }
 
 int pat_tree_build_ragged(pat_tree* t, const int32_t* seq_lens, const int32_t* flat_pages,
                           const int64_t* offsets, int num_seqs) {
     if (!t) return PAT_ERR_BAD_ARGUMENT;
-    return t->tree.build_ragged(seq_lens, flat_pages, offsets, num_seqs);
+    try {
+        return t->tree.build_ragged(seq_lens, flat_pages, offsets, num_seqs);
+    } catch (...) { return PAT_ERR_NO_MEMORY; }
 }
 
 int pat_tree_pack(pat_tree* t, const int32_t* mnws, int num_mnws, int hratio, int kv_heads,
                   int use_compute_model) {
     if (!t) return PAT_ERR_BAD_ARGUMENT;
-    return t->tree.pack(mnws, num_mnws, hratio, kv_heads, use_compute_model != 0);
+    try {
+        return t->tree.pack(mnws, num_mnws, hratio, kv_heads, use_compute_model != 0);
+    } catch (...) { return PAT_ERR_NO_MEMORY; }
 }
 
 int pat_tree_num_buckets(const pat_tree* t) { return t ? static_cast<int>(t->tree.buckets().size()) : 0; }
@@ -159,9 +166,11 @@ int pat_tree_node_pages(const pat_tree* t, int node, const int32_t** pages, int*
 
 int pat_tree_node_children(const pat_tree* t, int node, int32_t* out, int cap) {
     if (!t || node < 0 || node >= static_cast<int>(t->tree.nodes().size())) return PAT_ERR_BAD_ARGUMENT;
-    const std::vector<int> kids = t->tree.children_in_order(node);
-    for (int i = 0; i < static_cast<int>(kids.size()) && i < cap; ++i) out[i] = kids[i];
-    return static_cast<int>(kids.size());
+    try {
+        const std::vector<int> kids = t->tree.children_in_order(node);
+        for (int i = 0; i < static_cast<int>(kids.size()) && i < cap; ++i) out[i] = kids[i];
+        return static_cast<int>(kids.size());
+    } catch (...) { return PAT_ERR_NO_MEMORY; }
 }
 
 pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int batch, int hratio,
@@ -170,7 +179,8 @@ pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int b
     int dummy;
     if (!status) status = &dummy;
     pat_work* w = new (std::nothrow) pat_work();
-    if (!w) { *status = PAT_ERR_BAD_ARGUMENT; return nullptr; }
+    if (!w) { *status = PAT_ERR_NO_MEMORY; return nullptr; }
+    try {
     std::vector<pat::PlanBucketView> views(num_buckets > 0 ? num_buckets : 0);
     for (int i = 0; i < num_buckets; ++i) {
         views[i].ctas = buckets[i].ctas;
@@ -186,6 +196,11 @@ pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int b
     *status = map_work_error(rc);
     if (rc != 0) { delete w; return nullptr; }
     return w;
+    } catch (...) {
+        delete w;
+        *status = PAT_ERR_NO_MEMORY;
+        return nullptr;
+    }
 }
 
 pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_t num_cache_pages,
@@ -193,6 +208,7 @@ pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_
     int dummy;
     if (!status) status = &dummy;
     if (!t) { *status = PAT_ERR_BAD_ARGUMENT; return nullptr; }
+    try {
     const auto& bks = t->tree.buckets();
     std::vector<pat_plan_bucket> views(bks.size());
     for (size_t i = 0; i < bks.size(); ++i) {
@@ -207,6 +223,10 @@ pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_
     }
     return pat_work_create(views.data(), static_cast<int>(views.size()), t->tree.batch(), hratio, kv_heads,
                            t->tree.block_size(), num_cache_pages, options, status);
+    } catch (...) {
+        *status = PAT_ERR_NO_MEMORY;
+        return nullptr;
+    }
 }
 
 void pat_work_destroy(pat_work* w) { delete w; }
