@@ -186,7 +186,7 @@ def main():
             vv = (torch.randn(L, w.num_kv_heads, D, generator=g) * 0.5).to(dt).float()
             return kk, vv
 
-        total_budget = 100.0
+        total_budget = 60.0
         per_step = max(1.0, total_budget / max(1, args.steps + args.warmup))
         vals = []
         for step in range(args.warmup + args.steps):
