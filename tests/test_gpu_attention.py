@@ -291,6 +291,40 @@ def test_async_tree_and_strided_views_like_the_serving_backend(native_lib):
     _assert_close(decode_output.float().cpu(), lse.cpu(), ref_o[:, 0], ref_l, dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_against_flash_attention_like_the_reference_test(dtype, native_lib):
+    """The reference checks itself against flash-attention's paged decode kernel with
+    max |PAT - FlashAttention| <= 1e-2 (test/test.py:64, 150-165).  Same check here, on 256-token
+    pages (the page size the installed flash-attention accepts); skipped where that library does
+    not load or cannot run."""
+    try:
+        from flash_attn import flash_attn_with_kvcache
+    except Exception as exc:
+        pytest.skip(f"flash_attn is not available: {exc}")
+    page, hq, hk, d = 256, 32, 8, 128
+    rng = np.random.default_rng(0)
+    tables, lens, nxt = [], [], 0
+    for _ in range(3):                                   # 3 groups of 8 requests sharing 2 pages
+        shared = [nxt, nxt + 1]
+        nxt += 2
+        for _ in range(8):
+            n = int(rng.integers(1, 4))
+            tables.append(shared + list(range(nxt, nxt + n)))
+            nxt += n
+            lens.append(len(tables[-1]) * page - int(rng.integers(0, 255)))
+    q, k, v = _values(nxt, page, hq, hk, d, len(lens), dtype, 3)
+    scale = 1.0 / math.sqrt(d)
+    out, _, _ = _run_tree(q, k, v, lens, tables, page, hq // hk, hk, scale)
+    try:
+        ref = flash_attn_with_kvcache(q.to(DEV), k.to(DEV), v.to(DEV),
+                                      cache_seqlens=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                                      block_table=_padded(tables).to(DEV), softmax_scale=scale, causal=True)
+        torch.cuda.synchronize()
+    except Exception as exc:
+        pytest.skip(f"flash_attn could not run here: {exc}")
+    assert (ref.float().cpu()[:, 0] - out).abs().max().item() <= 1e-2
+
+
 def test_garbage_beyond_the_valid_tokens_is_ignored(native_lib):
     """Cache rows past a request's length may hold anything (NaN included)."""
     page, hq, hk, d = 16, 16, 2, 128
