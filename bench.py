@@ -48,6 +48,9 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA graph replays")
+    ap.add_argument("--flash-attn-baseline", action="store_true",
+                    help="also time flash_attn_with_kvcache (no prefix sharing) on the same requests laid out in "
+                         "256-token pages, next to this engine on that layout; one GPU, adds a JSON key")
     ap.add_argument("--emulate-shards", type=int, default=0,
                     help="with one GPU: run the work one rank of an S-GPU run would get (S KV-head shards)")
     ap.add_argument("--flags", type=int, default=0, help="extra launch flags (include/pat_b200.h), e.g. 16 = no overlap")
@@ -113,6 +116,89 @@ class ClockSampler:
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
                 "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "", 1).isdigit() else None,
                 "reasons": reasons, "samples": len(rows)}
+
+
+def flash_attn_baseline(w, hk, hq, D, dt, dev, scale):
+    """Context number, not the reference: the flash-attention library's paged decode kernel, which
+    reads every request's whole context (no prefix sharing), against this engine on the same
+    requests.  That library wants 256-token pages, so both run on a 256-token-page rendition of the
+    workload (same lengths, same sharing: a request keeps its group's pages for as long as its
+    16-token pages were shared)."""
+    import torch
+    from pat_b200 import PrefixTreeCPP, prefix_attn_with_kvcache
+    try:
+        from flash_attn import flash_attn_with_kvcache
+    except Exception as exc:
+        return {"unavailable": f"flash_attn does not load: {exc}"}
+    page, old = 256, w.page_size
+    owners = {}
+    for t in w.block_tables:
+        for pid in t:
+            owners[pid] = owners.get(pid, 0) + 1
+    tables, shared, nxt = [], {}, 0
+    for b, L in enumerate(w.seq_lens):
+        t16 = w.block_tables[b]
+        n_shared16 = 0
+        while n_shared16 < len(t16) and owners[t16[n_shared16]] > 1:
+            n_shared16 += 1
+        n_shared = (n_shared16 * old) // page               # whole 256-token pages inside the shared run
+        key = t16[0]
+        row = []
+        if n_shared:
+            if key not in shared:
+                shared[key] = list(range(nxt, nxt + n_shared))
+                nxt += n_shared
+            row = list(shared[key][:n_shared])
+        own = -(-L // page) - len(row)
+        row += list(range(nxt, nxt + own))
+        nxt += own
+        tables.append(row)
+    B = len(tables)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    q = (torch.randn(B, 1, hq, D, generator=gen, device=dev) * 0.5).to(dt)
+    k = torch.empty(nxt, page, hk, D, dtype=dt, device=dev)
+    v = torch.empty_like(k)
+    for lo in range(0, nxt, 256):
+        hi = min(nxt, lo + 256)
+        k[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
+        v[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
+    table = torch.zeros(B, max(len(t) for t in tables), dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    tree = PrefixTreeCPP(page)
+    tree.build_radix_tree(list(w.seq_lens), table)
+    tree.pack_schedule(None, hq // hk, hk)
+    tree.kernel_info.to_gpu(dev)
+    out = torch.empty_like(q)
+    td, ld = table.to(dev), torch.tensor(list(w.seq_lens), dtype=torch.int32, device=dev)
+
+    def ours():
+        prefix_attn_with_kvcache(q, k, v, tree, scale, out)
+
+    def lib():
+        return flash_attn_with_kvcache(q, k, v, cache_seqlens=ld, block_table=td, softmax_scale=scale, causal=True)
+
+    def timed(fn, iters=20):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    try:
+        ref = lib()
+        ours()
+        torch.cuda.synchronize()
+        diff = (ref.float() - out.float()).abs().max().item()
+        return {"page_size": page, "pages": nxt, "us_this_engine": timed(ours), "us_flash_attn_with_kvcache": timed(lib),
+                "max_abs_diff": diff, "timing": "direct launches, CUDA events, 20 steps"}
+    except Exception as exc:
+        return {"unavailable": f"flash_attn could not run: {exc}"}
 
 
 def cpu_attention_sample(w, q_cpu, k_rows, budget_s, order):
@@ -382,6 +468,10 @@ def main():
             dist.destroy_process_group()
         return
 
+    library_baseline = None
+    if args.flash_attn_baseline and n == 1:
+        library_baseline = flash_attn_baseline(w, hk, hq, D, dt, dev, scale)
+
     peak, peak_kind = measured_peak()
     elt = 2
     kv_bytes = lambda tokens: 2 * tokens * hk * D * elt
@@ -421,6 +511,7 @@ def main():
                  "entries": hdr.num_entries, "segments": hdr.num_segments,
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
         "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},
+        **({"flash_attn_baseline": library_baseline} if library_baseline else {}),
         "append_kv": {"us": append_ms * 1e3, "tokens": B, "bytes": int(2 * 2 * B * hk * D * elt),
                       "note": "KV-cache append of one token per request (separate launch, not part of value)"},
     }
