@@ -48,9 +48,10 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA graph replays")
-    ap.add_argument("--flash-attn-baseline", action="store_true",
-                    help="also time flash_attn_with_kvcache (no prefix sharing) on the same requests laid out in "
-                         "256-token pages, next to this engine on that layout; one GPU, adds a JSON key")
+    ap.add_argument("--library-baselines", action="store_true",
+                    help="also time two library decode kernels that know nothing of shared prefixes: FlashInfer's "
+                         "paged batch decode on this workload as is, and flash_attn_with_kvcache on the same requests "
+                         "laid out in 256-token pages; one GPU, adds JSON keys")
     ap.add_argument("--emulate-shards", type=int, default=0,
                     help="with one GPU: run the work one rank of an S-GPU run would get (S KV-head shards)")
     ap.add_argument("--flags", type=int, default=0, help="extra launch flags (include/pat_b200.h), e.g. 16 = no overlap")
@@ -116,6 +117,46 @@ class ClockSampler:
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
                 "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "", 1).isdigit() else None,
                 "reasons": reasons, "samples": len(rows)}
+
+
+def flashinfer_baseline(w, q, k_cache, v_cache, out, scale):
+    """Context number, not the reference: FlashInfer's paged batch decode (tensor-core path) on the
+    bench's own tensors.  It attends every request's whole context; shared pages are re-read per
+    request (mostly from L2).  `out` holds this engine's result for the same inputs."""
+    import torch
+    try:
+        import flashinfer
+    except Exception as exc:
+        return {"unavailable": f"flashinfer does not load: {exc}"}
+    dev = q.device
+    page, hk, hq, D = k_cache.shape[1], k_cache.shape[2], q.shape[2], q.shape[3]
+    indptr, indices, last = [0], [], []
+    for L, t in zip(w.seq_lens, w.block_tables):
+        npg = -(-L // page)
+        indices += t[:npg]
+        indptr.append(indptr[-1] + npg)
+        last.append(L - (npg - 1) * page)
+    try:
+        ws = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+        wrap = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD", use_tensor_cores=True)
+        wrap.plan(torch.tensor(indptr, dtype=torch.int32, device=dev), torch.tensor(indices, dtype=torch.int32, device=dev),
+                  torch.tensor(last, dtype=torch.int32, device=dev), hq, hk, D, page, q_data_type=q.dtype, sm_scale=scale)
+        q3 = q[:, 0]
+        res = wrap.run(q3, (k_cache, v_cache))
+        for _ in range(3):
+            wrap.run(q3, (k_cache, v_cache))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            wrap.run(q3, (k_cache, v_cache))
+        e1.record()
+        torch.cuda.synchronize()
+        return {"version": getattr(flashinfer, "__version__", "?"), "us_batch_decode_tensor_cores": e0.elapsed_time(e1) / 10 * 1e3,
+                "max_abs_diff": (res.float() - out[:, 0].float()).abs().max().item(),
+                "timing": "direct launches, CUDA events, 10 steps; plan() outside the timed region"}
+    except Exception as exc:
+        return {"unavailable": f"flashinfer could not run: {exc}"}
 
 
 def flash_attn_baseline(w, hk, hq, D, dt, dev, scale):
@@ -468,8 +509,9 @@ def main():
             dist.destroy_process_group()
         return
 
-    library_baseline = None
-    if args.flash_attn_baseline and n == 1:
+    library_baseline = flashinfer_line = None
+    if args.library_baselines and n == 1:
+        flashinfer_line = flashinfer_baseline(w, q, k_cache, v_cache, out, scale)
         library_baseline = flash_attn_baseline(w, hk, hq, D, dt, dev, scale)
 
     peak, peak_kind = measured_peak()
@@ -511,6 +553,7 @@ def main():
                  "entries": hdr.num_entries, "segments": hdr.num_segments,
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
         "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},
+        **({"flashinfer_baseline": flashinfer_line} if flashinfer_line else {}),
         **({"flash_attn_baseline": library_baseline} if library_baseline else {}),
         "append_kv": {"us": append_ms * 1e3, "tokens": B, "bytes": int(2 * 2 * B * hk * D * elt),
                       "note": "KV-cache append of one token per request (separate launch, not part of value)"},
