@@ -498,10 +498,27 @@ def main():
     wall2 = time.time()
     sampler.stop()
 
-    vals = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    # The one optional collective: every rank gets the other ranks' heads (NCCL all-gather).  A
+    # tensor-parallel model consumes the shard locally instead, so it is not part of `value`.
+    gather_ms = 0.0
+    if n > 1:
+        from pat_b200.sharding import all_gather_heads
+        for _ in range(3):
+            full = all_gather_heads(out, n)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            full = all_gather_heads(out, n)
+        e1.record()
+        torch.cuda.synchronize()
+        gather_ms = e0.elapsed_time(e1) / 10
+        assert tuple(full.shape) == (B, 1, hq * n, D)
+
+    vals = torch.tensor([ms, e2e_ms, gather_ms], dtype=torch.float64, device=dev)
     if n > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = vals.tolist()
+    ms, e2e_ms, gather_ms = vals.tolist()
 
     if rank != 0:
         if n > 1:
@@ -553,6 +570,9 @@ def main():
                  "entries": hdr.num_entries, "segments": hdr.num_segments,
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
         "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},
+        **({"all_gather_outputs": {"us": gather_ms * 1e3, "bytes_per_rank": int(out.numel() * elt),
+                                   "note": "optional NCCL all-gather of the output heads; not part of value"}}
+           if n > 1 else {}),
         **({"flashinfer_baseline": flashinfer_line} if flashinfer_line else {}),
         **({"flash_attn_baseline": library_baseline} if library_baseline else {}),
         "append_kv": {"us": append_ms * 1e3, "tokens": B, "bytes": int(2 * 2 * B * hk * D * elt),
