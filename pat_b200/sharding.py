@@ -40,9 +40,11 @@ def all_gather_heads(out_shard: torch.Tensor, world: int, group=None) -> torch.T
     if world == 1:
         return out_shard
     import torch.distributed as dist
-    parts = [torch.empty_like(out_shard) for _ in range(world)]
-    dist.all_gather(parts, out_shard.contiguous(), group=group)
-    return torch.cat(parts, dim=2)
+    shard = out_shard.contiguous()
+    buf = torch.empty((world,) + tuple(shard.shape), dtype=shard.dtype, device=shard.device)
+    dist.all_gather_into_tensor(buf.view(world * shard.shape[0], *shard.shape[1:]), shard, group=group)
+    b, one, h, d = shard.shape
+    return buf.permute(1, 2, 0, 3, 4).reshape(b, one, world * h, d)      # rank-major head order
 
 
 class ShardedDecode:
