@@ -379,8 +379,10 @@ def main():
         flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
         flush_rd = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
 
+    status = torch.zeros(4, dtype=torch.int32, device=dev)     # set by a kernel whose bounded wait gave up
+
     def step(flags=0):
-        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags | args.flags)
+        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags | args.flags, _status=status)
 
     def barrier():
         torch.cuda.synchronize()
@@ -497,6 +499,8 @@ def main():
         torch.cuda.synchronize()
     wall2 = time.time()
     sampler.stop()
+    if int(status[0].item()) != 0:
+        raise RuntimeError(f"a kernel reported a failed wait (status {status.tolist()}); the timings are void")
 
     # The one optional collective: every rank gets the other ranks' heads (NCCL all-gather).  A
     # tensor-parallel model consumes the shard locally instead, so it is not part of `value`.
