@@ -152,11 +152,66 @@ def flashinfer_baseline(w, q, k_cache, v_cache, out, scale):
             wrap.run(q3, (k_cache, v_cache))
         e1.record()
         torch.cuda.synchronize()
-        return {"version": getattr(flashinfer, "__version__", "?"), "us_batch_decode_tensor_cores": e0.elapsed_time(e1) / 10 * 1e3,
+        line = {"version": getattr(flashinfer, "__version__", "?"), "us_batch_decode_tensor_cores": e0.elapsed_time(e1) / 10 * 1e3,
                 "max_abs_diff": (res.float() - out[:, 0].float()).abs().max().item(),
                 "timing": "direct launches, CUDA events, 10 steps; plan() outside the timed region"}
     except Exception as exc:
         return {"unavailable": f"flashinfer could not run: {exc}"}
+    # The library's own prefix-aware path: two-level cascade attention (level 0 = the pages a group
+    # of requests shares, attended once for the whole group; level 1 = every request's own pages).
+    try:
+        groups = {}
+        for b, t in enumerate(w.block_tables):
+            groups.setdefault(t[0], []).append(b)
+        groups = sorted(groups.values(), key=lambda m: m[0])
+        order = [b for m in groups for b in m]              # the queries of a group must be contiguous
+        owners = {}
+        for t in w.block_tables:
+            for pid in t:
+                owners[pid] = owners.get(pid, 0) + 1
+        lv = [dict(qo=[0], ptr=[0], idx=[], last=[]) for _ in range(2)]
+        for m in groups:
+            t = w.block_tables[m[0]]
+            ns = 1                                          # an unshared request: its first page is "level 0"
+            if len(m) > 1:
+                ns = 0
+                while ns < len(t) and owners[t[ns]] > 1:
+                    ns += 1
+            lv[0]["idx"] += t[:ns]
+            lv[0]["ptr"].append(lv[0]["ptr"][-1] + ns)
+            lv[0]["last"].append(page)
+            lv[0]["qo"].append(lv[0]["qo"][-1] + len(m))
+            for b in m:
+                L = w.seq_lens[b]
+                npg = -(-L // page)
+                own = w.block_tables[b][ns:npg]
+                if not own:
+                    raise ValueError("a request without pages of its own")
+                lv[1]["idx"] += own
+                lv[1]["ptr"].append(lv[1]["ptr"][-1] + len(own))
+                lv[1]["last"].append(L - (npg - 1) * page)
+                lv[1]["qo"].append(lv[1]["qo"][-1] + 1)
+        ti = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        ws2 = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+        casc = flashinfer.MultiLevelCascadeAttentionWrapper(2, ws2, "NHD")
+        casc.plan([ti(l["qo"]) for l in lv], [ti(l["ptr"]) for l in lv], [ti(l["idx"]) for l in lv],
+                  [ti(l["last"]) for l in lv], hq, hk, D, page, causal=False, sm_scale=scale, q_data_type=q.dtype)
+        perm = torch.tensor(order, device=dev)
+        qs = q[:, 0][perm].contiguous()
+        res = casc.run(qs, (k_cache, v_cache))
+        for _ in range(3):
+            casc.run(qs, (k_cache, v_cache))
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(10):
+            casc.run(qs, (k_cache, v_cache))
+        e1.record()
+        torch.cuda.synchronize()
+        line["us_cascade_two_levels"] = e0.elapsed_time(e1) / 10 * 1e3
+        line["cascade_max_abs_diff"] = (res.float() - out[:, 0][perm].float()).abs().max().item()
+    except Exception as exc:
+        line["cascade_unavailable"] = str(exc)[:200]
+    return line
 
 
 def flash_attn_baseline(w, hk, hq, D, dt, dev, scale):
