@@ -173,10 +173,16 @@ def flashinfer_baseline(w, q, k_cache, v_cache, out, scale):
         for m in groups:
             t = w.block_tables[m[0]]
             ns = 1                                          # an unshared request: its first page is "level 0"
-            if len(m) > 1:
-                ns = 0
-                while ns < len(t) and owners[t[ns]] > 1:
-                    ns += 1
+            if len(m) > 1:                                  # the pages common to every request of the group
+                ns = min(len(w.block_tables[b]) for b in m)
+                for b in m[1:]:
+                    tb = w.block_tables[b]
+                    i = 0
+                    while i < ns and tb[i] == t[i]:
+                        i += 1
+                    ns = i
+                # every request keeps at least one page of its own for level 1
+                ns = min(ns, min(-(-w.seq_lens[b] // page) for b in m) - 1)
             lv[0]["idx"] += t[:ns]
             lv[0]["ptr"].append(lv[0]["ptr"][-1] + ns)
             lv[0]["last"].append(page)
