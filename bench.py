@@ -10,14 +10,20 @@ ranks; there is no data-path collective.  Rank 0 prints one JSON line.
 
 A "step" is one call of the public op ``prefix_attn_with_kvcache`` (all kernels of one decode
 step of one layer) on the same resident paged KV cache.  ``value`` times the kernels with CUDA
-events; ``e2e`` additionally moves the step's host inputs (queries, plan tables / work list)
-to the device and the output back inside the timed region.  The KV cache itself is state that
-lives on the GPU across steps (a decode step appends one token per request), so it is not
-copied per step.
+events; ``e2e`` additionally moves the step's host inputs (queries, work list) to the device and
+the output back inside the timed region.  The KV cache itself is state that lives on the GPU
+across steps (a decode step appends one token per request), so it is not copied per step.
+
+After the timed regions every rank recomputes a seeded sample of requests with the fp32 CPU
+oracle from the K/V values it reads back from its own GPU and compares the output and the LSE of
+one more (replayed) step with them (``parity_check``); a mismatch makes the run exit non-zero,
+like the PASSED/FAILED line of the reference's own kernel benchmark
+(``benchmark/benchmark_kernel.py:55-70, 271-279``).
 
 ``--impl reference`` times the reference's own attention path - dense fp32 PyTorch attention
-per request on the host cores (the CPU restatement in oracle/attention_oracle.py of
-test/utils.py::attention_ref) - on a bounded sample of the same workload.
+per request on the host cores (``test/utils.py::attention_ref`` itself when a reference checkout
+is present, else its CPU restatement in oracle/attention_oracle.py) - on a bounded sample of the
+same workload, with all host cores.
 """
 from __future__ import annotations
 
@@ -25,6 +31,7 @@ import argparse
 import json
 import math
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -36,6 +43,9 @@ if ROOT not in sys.path:
 
 METRIC = "decode_attn_us_per_step"
 UNIT = "us"
+TRAFFIC_FILE = os.path.join("profiles", "dram_traffic.json")
+TOL = {"bf16": 2e-2, "fp16": 1e-2}
+LSE_TOL = 1e-3
 
 
 def parse():
@@ -48,15 +58,13 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA graph replays")
-    ap.add_argument("--library-baselines", action="store_true",
-                    help="also time two library decode kernels that know nothing of shared prefixes: FlashInfer's "
-                         "paged batch decode on this workload as is, and flash_attn_with_kvcache on the same requests "
-                         "laid out in 256-token pages; one GPU, adds JSON keys")
     ap.add_argument("--emulate-shards", type=int, default=0,
                     help="with one GPU: run the work one rank of an S-GPU run would get (S KV-head shards)")
     ap.add_argument("--flags", type=int, default=0, help="extra launch flags (include/pat_b200.h), e.g. 16 = no overlap")
     ap.add_argument("--scale-down", type=int, default=1,
                     help="divide every segment length by this factor (profiling captures on a small case)")
+    ap.add_argument("--parity-requests", type=int, default=8, help="requests every rank checks against the oracle")
+    ap.add_argument("--plan-repeats", type=int, default=20, help="warm repeats of the plan build (median reported)")
     return ap.parse_args()
 
 
@@ -67,6 +75,17 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def traffic_record(config: int, scale_down: int, kernel: str):
+    """DRAM traffic of one launch as a ratio to its algorithmic bytes, from the tracked summary
+    of ncu captures; ``None`` when this workload's kernel has not been captured."""
+    try:
+        with open(os.path.join(ROOT, TRAFFIC_FILE)) as f:
+            table = json.load(f)
+    except Exception:
+        return None
+    return table.get("captures", {}).get(f"cfg{config}", {}).get(kernel)
 
 
 class ClockSampler:
@@ -119,207 +138,70 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows)}
 
 
-def flashinfer_baseline(w, q, k_cache, v_cache, out, scale):
-    """Context number, not the reference: FlashInfer's paged batch decode (tensor-core path) on the
-    bench's own tensors.  It attends every request's whole context; shared pages are re-read per
-    request (mostly from L2).  `out` holds this engine's result for the same inputs."""
-    import torch
-    try:
-        import flashinfer
-    except Exception as exc:
-        return {"unavailable": f"flashinfer does not load: {exc}"}
-    dev = q.device
-    page, hk, hq, D = k_cache.shape[1], k_cache.shape[2], q.shape[2], q.shape[3]
-    indptr, indices, last = [0], [], []
-    for L, t in zip(w.seq_lens, w.block_tables):
-        npg = -(-L // page)
-        indices += t[:npg]
-        indptr.append(indptr[-1] + npg)
-        last.append(L - (npg - 1) * page)
-    try:
-        ws = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-        wrap = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD", use_tensor_cores=True)
-        wrap.plan(torch.tensor(indptr, dtype=torch.int32, device=dev), torch.tensor(indices, dtype=torch.int32, device=dev),
-                  torch.tensor(last, dtype=torch.int32, device=dev), hq, hk, D, page, q_data_type=q.dtype, sm_scale=scale)
-        q3 = q[:, 0]
-        res = wrap.run(q3, (k_cache, v_cache))
-        for _ in range(3):
-            wrap.run(q3, (k_cache, v_cache))
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(10):
-            wrap.run(q3, (k_cache, v_cache))
-        e1.record()
-        torch.cuda.synchronize()
-        line = {"version": getattr(flashinfer, "__version__", "?"), "us_batch_decode_tensor_cores": e0.elapsed_time(e1) / 10 * 1e3,
-                "max_abs_diff": (res.float() - out[:, 0].float()).abs().max().item(),
-                "timing": "direct launches, CUDA events, 10 steps; plan() outside the timed region"}
-    except Exception as exc:
-        return {"unavailable": f"flashinfer could not run: {exc}"}
-    # The library's own prefix-aware path: two-level cascade attention (level 0 = the pages a group
-    # of requests shares, attended once for the whole group; level 1 = every request's own pages).
-    try:
-        groups = {}
-        for b, t in enumerate(w.block_tables):
-            groups.setdefault(t[0], []).append(b)
-        groups = sorted(groups.values(), key=lambda m: m[0])
-        order = [b for m in groups for b in m]              # the queries of a group must be contiguous
-        owners = {}
-        for t in w.block_tables:
-            for pid in t:
-                owners[pid] = owners.get(pid, 0) + 1
-        lv = [dict(qo=[0], ptr=[0], idx=[], last=[]) for _ in range(2)]
-        for m in groups:
-            t = w.block_tables[m[0]]
-            ns = 1                                          # an unshared request: its first page is "level 0"
-            if len(m) > 1:                                  # the pages common to every request of the group
-                ns = min(len(w.block_tables[b]) for b in m)
-                for b in m[1:]:
-                    tb = w.block_tables[b]
-                    i = 0
-                    while i < ns and tb[i] == t[i]:
-                        i += 1
-                    ns = i
-                # every request keeps at least one page of its own for level 1
-                ns = min(ns, min(-(-w.seq_lens[b] // page) for b in m) - 1)
-            lv[0]["idx"] += t[:ns]
-            lv[0]["ptr"].append(lv[0]["ptr"][-1] + ns)
-            lv[0]["last"].append(page)
-            lv[0]["qo"].append(lv[0]["qo"][-1] + len(m))
-            for b in m:
-                L = w.seq_lens[b]
-                npg = -(-L // page)
-                own = w.block_tables[b][ns:npg]
-                if not own:
-                    raise ValueError("a request without pages of its own")
-                lv[1]["idx"] += own
-                lv[1]["ptr"].append(lv[1]["ptr"][-1] + len(own))
-                lv[1]["last"].append(L - (npg - 1) * page)
-                lv[1]["qo"].append(lv[1]["qo"][-1] + 1)
-        ti = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
-        ws2 = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-        casc = flashinfer.MultiLevelCascadeAttentionWrapper(2, ws2, "NHD")
-        casc.plan([ti(l["qo"]) for l in lv], [ti(l["ptr"]) for l in lv], [ti(l["idx"]) for l in lv],
-                  [ti(l["last"]) for l in lv], hq, hk, D, page, causal=False, sm_scale=scale, q_data_type=q.dtype)
-        perm = torch.tensor(order, device=dev)
-        qs = q[:, 0][perm].contiguous()
-        res = casc.run(qs, (k_cache, v_cache))
-        for _ in range(3):
-            casc.run(qs, (k_cache, v_cache))
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(10):
-            casc.run(qs, (k_cache, v_cache))
-        e1.record()
-        torch.cuda.synchronize()
-        line["us_cascade_two_levels"] = e0.elapsed_time(e1) / 10 * 1e3
-        line["cascade_max_abs_diff"] = (res.float() - out[:, 0][perm].float()).abs().max().item()
-    except Exception as exc:
-        line["cascade_unavailable"] = str(exc)[:200]
-    return line
-
-
-def flash_attn_baseline(w, hk, hq, D, dt, dev, scale):
-    """Context number, not the reference: the flash-attention library's paged decode kernel, which
-    reads every request's whole context (no prefix sharing), against this engine on the same
-    requests.  That library wants 256-token pages, so both run on a 256-token-page rendition of the
-    workload (same lengths, same sharing: a request keeps its group's pages for as long as its
-    16-token pages were shared)."""
-    import torch
-    from pat_b200 import PrefixTreeCPP, prefix_attn_with_kvcache
-    try:
-        from flash_attn import flash_attn_with_kvcache
-    except Exception as exc:
-        return {"unavailable": f"flash_attn does not load: {exc}"}
-    page, old = 256, w.page_size
-    owners = {}
-    for t in w.block_tables:
-        for pid in t:
-            owners[pid] = owners.get(pid, 0) + 1
-    tables, shared, nxt = [], {}, 0
-    for b, L in enumerate(w.seq_lens):
-        t16 = w.block_tables[b]
-        n_shared16 = 0
-        while n_shared16 < len(t16) and owners[t16[n_shared16]] > 1:
-            n_shared16 += 1
-        n_shared = (n_shared16 * old) // page               # whole 256-token pages inside the shared run
-        key = t16[0]
-        row = []
-        if n_shared:
-            if key not in shared:
-                shared[key] = list(range(nxt, nxt + n_shared))
-                nxt += n_shared
-            row = list(shared[key][:n_shared])
-        own = -(-L // page) - len(row)
-        row += list(range(nxt, nxt + own))
-        nxt += own
-        tables.append(row)
-    B = len(tables)
-    gen = torch.Generator(device=dev).manual_seed(7)
-    q = (torch.randn(B, 1, hq, D, generator=gen, device=dev) * 0.5).to(dt)
-    k = torch.empty(nxt, page, hk, D, dtype=dt, device=dev)
-    v = torch.empty_like(k)
-    for lo in range(0, nxt, 256):
-        hi = min(nxt, lo + 256)
-        k[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
-        v[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
-    table = torch.zeros(B, max(len(t) for t in tables), dtype=torch.int32)
-    for i, t in enumerate(tables):
-        table[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
-    tree = PrefixTreeCPP(page)
-    tree.build_radix_tree(list(w.seq_lens), table)
-    tree.pack_schedule(None, hq // hk, hk)
-    tree.kernel_info.to_gpu(dev)
-    out = torch.empty_like(q)
-    td, ld = table.to(dev), torch.tensor(list(w.seq_lens), dtype=torch.int32, device=dev)
-
-    def ours():
-        prefix_attn_with_kvcache(q, k, v, tree, scale, out)
-
-    def lib():
-        return flash_attn_with_kvcache(q, k, v, cache_seqlens=ld, block_table=td, softmax_scale=scale, causal=True)
-
-    def timed(fn, iters=20):
-        for _ in range(5):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / iters * 1e3
-
-    try:
-        ref = lib()
-        ours()
-        torch.cuda.synchronize()
-        diff = (ref.float() - out.float()).abs().max().item()
-        return {"page_size": page, "pages": nxt, "us_this_engine": timed(ours), "us_flash_attn_with_kvcache": timed(lib),
-                "max_abs_diff": diff, "timing": "direct launches, CUDA events, 20 steps"}
-    except Exception as exc:
-        return {"unavailable": f"flash_attn could not run: {exc}"}
-
-
-def cpu_attention_sample(w, q_cpu, k_rows, budget_s, order):
-    """Dense fp32 attention per request on the host cores for as many requests (in ``order``)
-    as fit in ``budget_s``.  ``k_rows(b)`` returns the request's dense (K, V) fp32 on the CPU.
-    Returns (seconds, tokens, requests)."""
-    import torch
+# --------------------------------------------------------------------------------------------
+# CPU legs (the only places where bench.py runs anything under oracle/)
+# --------------------------------------------------------------------------------------------
+def host_attention():
+    """(callable, kind): the reference's own ``attention_ref`` when its checkout is present
+    ("reference"), else the CPU restatement ("port").  Both take (q [1,1,H,D], k, v [1,S,Hkv,D])."""
     from oracle import attention_oracle as O
-    spent, tokens, done = 0.0, 0, 0
+    try:
+        from oracle import ref_loader
+        if os.path.isfile(os.path.join(ref_loader.REFERENCE_ROOT, "test", "utils.py")):
+            ref = ref_loader.load_reference_attention()
+            return (lambda q, k, v: ref(q, k, v)), "reference"
+    except Exception:
+        pass
+    return (lambda q, k, v: O.dense_attention(q, k, v, None, None)), "port"
+
+
+def pick_sample(w, budget_s: float, attend, q_cpu, rows):
+    """Requests (seeded order) whose dense fp32 attention takes about ``budget_s`` on this host:
+    the first request calibrates seconds per token.  Returns [(b, K, V)] with K/V fp32 on the CPU."""
+    import numpy as np
+    order = np.random.default_rng(w.seed).permutation(w.batch).tolist()
+    sample, tokens = [], 0
+    kk, vv = rows(order[0])
+    attend(q_cpu[order[0]:order[0] + 1], kk[None], vv[None])            # warm the thread pool
+    t0 = time.perf_counter()
+    attend(q_cpu[order[0]:order[0] + 1], kk[None], vv[None])
+    per_token = max((time.perf_counter() - t0) / max(1, w.seq_lens[order[0]]), 1e-9)
+    want_tokens = budget_s / per_token
     for b in order:
-        kk, vv = k_rows(b)
-        t0 = time.perf_counter()
-        O.dense_attention(q_cpu[b:b + 1], kk[None], vv[None], None, None)
-        spent += time.perf_counter() - t0
-        tokens += w.seq_lens[b]
-        done += 1
-        if spent >= budget_s:
+        if sample and tokens + w.seq_lens[b] > want_tokens:
             break
-    return spent, tokens, done
+        if b != order[0]:
+            kk, vv = rows(b)
+        sample.append((b, kk, vv))
+        tokens += w.seq_lens[b]
+    return sample, tokens
+
+
+def time_sample(sample, attend, q_cpu):
+    t0 = time.perf_counter()
+    for b, kk, vv in sample:
+        attend(q_cpu[b:b + 1], kk[None], vv[None])
+    return time.perf_counter() - t0
+
+
+def reference_scheduler_ms(w, hratio, kv_heads, repeats):
+    """Median milliseconds of the reference's own C++ scheduler (tree + pack) on this workload,
+    when the compiled checker is present; else None."""
+    try:
+        from oracle import ref_tree
+        if not ref_tree.available():
+            return None
+        import numpy as np
+        table = w.padded_table()
+        lens = np.asarray(w.seq_lens, dtype=np.int32)
+        times = []
+        for _ in range(max(3, repeats)):
+            t0 = time.perf_counter()
+            ref_tree.time_pack(lens, table, w.page_size, hratio, kv_heads)
+            times.append((time.perf_counter() - t0) * 1e3)
+        return statistics.median(times)
+    except Exception:
+        return None
 
 
 def main():
@@ -337,48 +219,52 @@ def main():
             sys.exit(2)
     n = world
 
-    from pat_b200.workloads import make_config, scaled_down, torch_dtype
+    from pat_b200.workloads import make_config, scaled_down, synthetic_pages, synthetic_queries, torch_dtype
     w = make_config(args.config) if args.scale_down <= 1 else scaled_down(args.config, args.scale_down)
     if w.num_kv_heads % n != 0 or (args.emulate_shards > 1 and w.num_kv_heads % args.emulate_shards != 0):
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "unavailable": f"{w.num_kv_heads} KV heads do not shard over {n} GPUs"}))
+            print(json.dumps({"metric": METRIC, "unavailable": f"{w.num_kv_heads} KV heads do not shard over {n} GPUs",
+                              **({"impl": "reference"} if args.impl == "reference" else {})}))
         return
     shards = args.emulate_shards if (n == 1 and args.emulate_shards > 1) else n
     hk = w.num_kv_heads // shards
     hq = hk * w.group
+    shard_rank = rank if shards == n else 0
+    heads = slice(shard_rank * hk, (shard_rank + 1) * hk)
     D, page, B = w.head_dim, w.page_size, w.batch
     scale = 1.0 / math.sqrt(D)
     dt = torch_dtype(w.dtype)
     workload_name = f"{w.name}: {w.description}; {w.num_q_heads}/{w.num_kv_heads} heads, D={D}, {w.dtype}, {page}-token pages"
-    config = {"workload": workload_name, "batch": B, "unique_tokens": w.unique_tokens,
-              "total_tokens": w.total_tokens, "kv_head_shards": shards,
-              "l2": "inputs larger than L2 (per-GPU KV bytes >> 126 MB); no flush between steps"}
     bytes_total = w.dedup_kv_bytes()
     bytes_rank = w.dedup_kv_bytes(kv_heads=hk, q_heads=hq)
-    if bytes_rank < 4 * 126e6:
-        config["l2"] = "per-GPU KV bytes are below 4x L2: between steps a 512 MB buffer is written and a 256 MB buffer read to flush L2"
+    small = bytes_rank < 4 * 126e6
+    config = {"workload": workload_name, "batch": B, "unique_tokens": w.unique_tokens,
+              "total_tokens": w.total_tokens, "kv_head_shards": shards,
+              "l2": ("per-GPU KV bytes are below 4x L2: between steps a 512 MB buffer is written and a 256 MB buffer "
+                     "read to flush L2") if small else
+                    "inputs larger than L2 (per-GPU KV bytes >> 126 MB); no flush between steps"}
 
     # ------------------------------------------------------------------ reference arm (CPU)
     if args.impl == "reference":
         if rank != 0:
             return
-        gen = torch.Generator().manual_seed(w.seed)
-        q_cpu = (torch.randn(B, 1, w.num_q_heads, D, generator=gen) * 0.5).to(dt).float()
-        rng = np.random.default_rng(0)
-        order = rng.permutation(B).tolist()
+        torch.set_num_threads(os.cpu_count() or 1)      # torchrun starts its workers with one thread
+        attend, kind = host_attention()
+        q_cpu = synthetic_queries(w).float()
 
         def rows(b):
-            g = torch.Generator().manual_seed(1000 + b)
             L = w.seq_lens[b]
-            kk = (torch.randn(L, w.num_kv_heads, D, generator=g) * 0.5).to(dt).float()
-            vv = (torch.randn(L, w.num_kv_heads, D, generator=g) * 0.5).to(dt).float()
+            ids = w.block_tables[b][:-(-L // page)]
+            kk = synthetic_pages(w, 0, ids).reshape(-1, w.num_kv_heads, D)[:L].float()
+            vv = synthetic_pages(w, 1, ids).reshape(-1, w.num_kv_heads, D)[:L].float()
             return kk, vv
 
-        total_budget = 60.0
-        per_step = max(1.0, total_budget / max(1, args.steps + args.warmup))
+        total_budget = 40.0
+        per_step = max(0.5, total_budget / max(1, args.steps + args.warmup))
+        sample, tok = pick_sample(w, per_step, attend, q_cpu, rows)
         vals = []
         for step in range(args.warmup + args.steps):
-            s, tok, done = cpu_attention_sample(w, q_cpu, rows, per_step, order[step % B:] + order[:step % B])
+            s = time_sample(sample, attend, q_cpu)
             if step >= args.warmup:
                 vals.append(s * w.total_tokens / tok)
         est = float(np.mean(vals))
@@ -387,9 +273,12 @@ def main():
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": est * 1e3,
                 "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
                 "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": est * 1e6, "unit": UNIT, "cores": cores, "kind": "port",
-                                 "sample": f"per step: as many whole requests as fit in {per_step:.1f} s of dense fp32 "
-                                           f"attention on the host, scaled to the workload by token count"},
+                "cpu_baseline": {"value": est * 1e6, "unit": UNIT, "cores": cores, "kind": kind,
+                                 "extrapolated": tok < w.total_tokens,
+                                 "sample": f"every step runs dense fp32 attention (the reference's PyTorch path) over the "
+                                           f"same {len(sample)} of {B} requests of this workload ({tok} of {w.total_tokens} "
+                                           f"context tokens, its own K/V values, about {per_step:.1f} s), and the time is "
+                                           f"scaled to the whole workload by token count"},
                 "e2e": {"value": est * 1e6, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line))
@@ -406,29 +295,40 @@ def main():
     from pat_b200 import PrefixTreeCPP, prefix_attn_with_kvcache
     from pat_b200 import _prefix_attn as P
 
-    gen = torch.Generator(device=dev).manual_seed(w.seed * 100 + rank)
-    q_host = (torch.randn(B, 1, hq, D, generator=torch.Generator().manual_seed(w.seed)) * 0.5).to(dt).pin_memory()
+    q_host = synthetic_queries(w, kv_heads=heads).pin_memory()
     k_cache = torch.empty(w.num_pages, page, hk, D, dtype=dt, device=dev)
     v_cache = torch.empty_like(k_cache)
     step_pages = 4096
     for lo in range(0, w.num_pages, step_pages):        # bounded temporaries
-        hi = min(w.num_pages, lo + step_pages)
-        k_cache[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
-        v_cache[lo:hi] = (torch.randn(hi - lo, page, hk, D, generator=gen, device=dev) * 0.5).to(dt)
+        ids = torch.arange(lo, min(w.num_pages, lo + step_pages), device=dev)
+        k_cache[lo:lo + step_pages] = synthetic_pages(w, 0, ids, dev, heads)
+        v_cache[lo:lo + step_pages] = synthetic_pages(w, 1, ids, dev, heads)
     q = q_host.to(dev)
     out = torch.empty_like(q)
+    lse = torch.empty(B, hq, dtype=torch.float32, device=dev)
     out_host = torch.empty(B, 1, hq, D, dtype=dt).pin_memory()
 
+    # ---- plan build: median of warm repeats (tree + pack on the host; work list + uploads)
     table = torch.from_numpy(w.padded_table())
+    lens_list = list(w.seq_lens)
     PrefixTreeCPP(page)                 # loads the library once, outside the plan-build timing
-    t0 = time.perf_counter()
-    tree = PrefixTreeCPP(page)
-    tree.build_radix_tree(list(w.seq_lens), table)
-    tree.pack_schedule(None, w.group, hk)
-    t1 = time.perf_counter()
-    tree.kernel_info.to_gpu(dev)
-    torch.cuda.synchronize()
-    t2 = time.perf_counter()
+    t_pack, t_work = [], []
+    tree = None
+    for _ in range(max(1, args.plan_repeats) + 1):
+        t0 = time.perf_counter()
+        tree = PrefixTreeCPP(page)
+        tree.build_radix_tree(lens_list, table)
+        tree.pack_schedule(None, w.group, hk)
+        t1 = time.perf_counter()
+        tree.kernel_info.to_gpu(dev)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        t_pack.append((t1 - t0) * 1e3)
+        t_work.append((t2 - t1) * 1e3)
+    plan_ms = {"tree_and_pack": statistics.median(t_pack[1:]) if len(t_pack) > 1 else t_pack[0],
+               "work_list_and_upload": statistics.median(t_work[1:]) if len(t_work) > 1 else t_work[0],
+               "first_call": {"tree_and_pack": t_pack[0], "work_list_and_upload": t_work[0]},
+               "repeats": len(t_pack) - 1, "statistic": "median of warm repeats"}
     work = tree.kernel_info.device_work(dev)
     hdr = work.header
 
@@ -436,14 +336,15 @@ def main():
     # the timed step starts with an L2 that holds none of its inputs and no dirty lines of the
     # flush itself (their write-back would otherwise run during the timed step).
     flush = flush_rd = None
-    if bytes_rank < 4 * 126e6:
+    if small:
         flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
         flush_rd = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
 
     status = torch.zeros(4, dtype=torch.int32, device=dev)     # set by a kernel whose bounded wait gave up
 
     def step(flags=0):
-        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, _flags=flags | args.flags, _status=status)
+        prefix_attn_with_kvcache(q, k_cache, v_cache, tree, scale, out, lse_out=lse,
+                                 _flags=flags | args.flags, _status=status)
 
     def barrier():
         torch.cuda.synchronize()
@@ -487,7 +388,6 @@ def main():
             torch.cuda.synchronize()
             return fn
 
-    launches_per_step = 0
     step()
     launches_per_step = P.last_launch_count()
     run_step = capture(step)
@@ -509,7 +409,14 @@ def main():
         ms = timed(run_step, args.steps)
         barrier()
     launches = launches_per_step * args.steps
-    wall1 = time.time()
+
+    # ---- parity: one more step of the timed kind (a graph replay), checked against the oracle
+    out.fill_(float("nan"))
+    lse.fill_(float("nan"))
+    run_step()
+    torch.cuda.synchronize()
+    out_checked = out.float().cpu()[:, 0]
+    lse_checked = lse.cpu()
 
     # per-kernel durations (each phase alone; same stream, CUDA events)
     reps = max(3, min(10, args.steps))
@@ -517,7 +424,7 @@ def main():
     if hdr.num_stream_items:
         k_ms["stream_kernel"] = timed(capture(lambda: step(2 | 4)), reps)
     if hdr.num_dense_items:
-        k_ms["dense_kernel"] = timed(capture(lambda: step(1 | 4)), reps)
+        k_ms["dense_tc_kernel"] = timed(capture(lambda: step(1 | 4)), reps)
     k_ms["merge_kernel"] = timed(capture(lambda: step(1 | 2)), reps)
     step()   # leave `out` complete
 
@@ -540,6 +447,12 @@ def main():
         torch.cuda.synchronize()
     for _ in range(3):
         e2e_step()
+    # host time of the Python call alone (argument checks, ctypes, three launches), kernels not awaited
+    torch.cuda.synchronize()
+    tc0 = time.perf_counter()
+    for _ in range(20):
+        step()
+    call_us = (time.perf_counter() - tc0) / 20 * 1e6
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     tw0 = time.perf_counter()
@@ -563,38 +476,66 @@ def main():
     if int(status[0].item()) != 0:
         raise RuntimeError(f"a kernel reported a failed wait (status {status.tolist()}); the timings are void")
 
-    # The one optional collective: every rank gets the other ranks' heads (NCCL all-gather).  A
-    # tensor-parallel model consumes the shard locally instead, so it is not part of `value`.
-    gather_ms = 0.0
+    # The one optional collective: every rank gets the other ranks' heads (NCCL all-gather into a
+    # buffer allocated once, then one small kernel of this library that puts the heads in order).
+    # A tensor-parallel model consumes the shard locally instead, so it is not part of `value`;
+    # `value_with_gather` times step + gather as one graph.
+    gather_ms = with_gather_ms = 0.0
     if n > 1:
-        from pat_b200.sharding import all_gather_heads
+        from pat_b200.sharding import HeadGather
+        hg = HeadGather(out, n)
         for _ in range(3):
-            full = all_gather_heads(out, n)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(10):
-            full = all_gather_heads(out, n)
-        e1.record()
-        torch.cuda.synchronize()
-        gather_ms = e0.elapsed_time(e1) / 10
+            full = hg(out)
+        barrier()
         assert tuple(full.shape) == (B, 1, hq * n, D)
+        run_gather = capture(lambda: hg(out))
+        gather_ms = timed(run_gather, 10)
+        barrier()
+        run_both = capture(lambda: (step(), hg(out)))
+        with_gather_ms = timed(run_both, max(5, min(20, args.steps)))
+        barrier()
+        # the gathered heads of rank r must be rank r's output: check our own block and one neighbour's checksum
+        mine = full[:, :, rank * hq:(rank + 1) * hq]
+        if not torch.equal(mine, out):
+            raise RuntimeError("all-gather of the output heads returned the wrong block for this rank")
 
-    vals = torch.tensor([ms, e2e_ms, gather_ms], dtype=torch.float64, device=dev)
+    # ---- parity check of the replayed step (every rank)
+    from oracle import attention_oracle as O
+    rng = np.random.default_rng(1000 * args.config + shard_rank)
+    picks = sorted(set(rng.choice(B, size=min(B, max(1, args.parity_requests)), replace=False).tolist()))
+    q_cpu = q_host.float()
+    tol = TOL[w.dtype]
+    max_err = max_lse = 0.0
+    ok = True
+    for b in picks:
+        L = w.seq_lens[b]
+        idx = torch.as_tensor(w.block_tables[b][:-(-L // page)], device=dev, dtype=torch.long)
+        kk = k_cache[idx].reshape(-1, hk, D)[:L].float().cpu()
+        vv = v_cache[idx].reshape(-1, hk, D)[:L].float().cpu()
+        ro, rl = O.dense_attention(q_cpu[b:b + 1], kk[None], vv[None], None, scale)
+        err = (out_checked[b] - ro[0, 0]).abs()
+        ok = ok and bool((err <= tol + tol * ro[0, 0].abs()).all())
+        lerr = (lse_checked[b] - rl[0, :, 0]).abs().max().item()
+        ok = ok and lerr <= LSE_TOL and bool(torch.isfinite(out_checked[b]).all())
+        max_err, max_lse = max(max_err, err.max().item()), max(max_lse, lerr)
+
+    vals = torch.tensor([ms, e2e_ms, gather_ms, with_gather_ms, max_err, max_lse, 0.0 if ok else 1.0, call_us],
+                        dtype=torch.float64, device=dev)
     if n > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, gather_ms = vals.tolist()
+    ms, e2e_ms, gather_ms, with_gather_ms, max_err, max_lse, bad, call_us = vals.tolist()
+    parity = {"requests": len(picks) * n, "requests_per_rank": len(picks), "max_abs_err": max_err,
+              "max_lse_err": max_lse, "atol_rtol": tol, "lse_tol": LSE_TOL, "ok": bad == 0.0,
+              "checked": "output and LSE of one more graph replay after the timed steps, against dense fp32 "
+                         "attention on the host over the K/V values read back from the GPU"}
 
     if rank != 0:
         if n > 1:
             dist.barrier()
             dist.destroy_process_group()
+        if not parity["ok"]:
+            sys.exit(3)
         return
-
-    library_baseline = flashinfer_line = None
-    if args.library_baselines and n == 1:
-        flashinfer_line = flashinfer_baseline(w, q, k_cache, v_cache, out, scale)
-        library_baseline = flash_attn_baseline(w, hk, hq, D, dt, dev, scale)
 
     peak, peak_kind = measured_peak()
     elt = 2
@@ -602,17 +543,17 @@ def main():
     dominant = max((k for k in k_ms if k != "merge_kernel"), key=lambda k_: k_ms[k_], default="merge_kernel")
     if dominant == "stream_kernel":
         alg = kv_bytes(hdr.stream_unique_tokens)
-    elif dominant == "dense_kernel":
+    elif dominant == "dense_tc_kernel":
         alg = kv_bytes(hdr.dense_unique_tokens)
     else:
         alg = hdr.num_entries * w.group * (D + 1) * 4 + B * hq * D * elt
     achieved = alg / (k_ms[dominant] * 1e-3) / 1e9
-    # DRAM traffic per launch: dram__bytes_read + dram__bytes_write of one ncu capture of the same
-    # kernels on this workload with all lengths / 4 (profiles/stream_dense_merge_cfg4_div4_full.md),
-    # as a ratio to the algorithmic bytes of that launch, scaled to this launch (the traffic of
-    # both kernels grows in proportion to the tokens they read).  Other workloads: not captured.
-    ncu_traffic_ratio = {"stream_kernel": 939.8 / 917.8, "dense_kernel": 127.8 / 117.4}
-    traffic = int(alg * ncu_traffic_ratio[dominant]) if (args.config == 4 and dominant in ncu_traffic_ratio) else None
+    # DRAM traffic per launch: dram__bytes_read + dram__bytes_write of an ncu capture of this kernel
+    # on a scaled-down case of this workload, as a ratio to the algorithmic bytes of that launch,
+    # scaled to this launch (the traffic grows in proportion to the tokens read).  The ratios and the
+    # captures they come from are kept in a tracked file, not here.
+    rec = traffic_record(args.config, args.scale_down, dominant)
+    traffic = int(alg * rec["traffic_over_algorithmic"]) if rec else None
     step_gbs = bytes_rank / (ms * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": ms * 1e3, "unit": UNIT, "n_gpus": n, "steps": args.steps,
@@ -622,10 +563,14 @@ def main():
                        window="timed steps, per-kernel and end-to-end loops, then 0.6 s of the same steps untimed"),
         "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
                 "h2d_bytes_per_step": int(q_host.numel() * elt + blob_host.numel() * 4),
-                "d2h_bytes_per_step": int(out_host.numel() * elt)},
+                "d2h_bytes_per_step": int(out_host.numel() * elt),
+                "python_call_us": call_us},
         "gpu_launches": launches,
+        "parity_check": parity,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
+                     "traffic_source": (f"{TRAFFIC_FILE}: {rec['capture']}" if rec else
+                                        f"no capture of {dominant} on this workload in {TRAFFIC_FILE}"),
                      "algorithmic_bytes_per_launch": alg, "kernel_ms": k_ms[dominant]},
         "step_roofline": {"dedup_bytes_per_gpu": bytes_rank, "dedup_bytes_total": bytes_total,
                           "achieved_gbs_per_gpu": step_gbs, "frac_of_measured_copy": step_gbs / peak,
@@ -634,20 +579,18 @@ def main():
         "work": {"stream_items": hdr.num_stream_items, "dense_items": hdr.num_dense_items, "dense_ctas": hdr.num_dense_ctas,
                  "entries": hdr.num_entries, "segments": hdr.num_segments,
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
-        "plan_build_ms": {"tree_and_pack": (t1 - t0) * 1e3, "work_list_and_upload": (t2 - t1) * 1e3},
+        "plan_build_ms": plan_ms,
         **({"all_gather_outputs": {"us": gather_ms * 1e3, "bytes_per_rank": int(out.numel() * elt),
-                                   "note": "optional NCCL all-gather of the output heads; not part of value"}}
-           if n > 1 else {}),
-        **({"flashinfer_baseline": flashinfer_line} if flashinfer_line else {}),
-        **({"flash_attn_baseline": library_baseline} if library_baseline else {}),
+                                   "note": "optional NCCL all-gather of the output heads + reorder kernel, graph replay; "
+                                           "not part of value"},
+            "value_with_gather": with_gather_ms * 1e3} if n > 1 else {}),
         "append_kv": {"us": append_ms * 1e3, "tokens": B, "bytes": int(2 * 2 * B * hk * D * elt),
                       "note": "KV-cache append of one token per request (separate launch, not part of value)"},
     }
 
     if n == 1 and not args.no_cpu_baseline:
-        q_cpu = q_host.float()
-        rng = np.random.default_rng(0)
-        order = rng.permutation(B).tolist()
+        torch.set_num_threads(os.cpu_count() or 1)
+        attend, kind = host_attention()
 
         def rows(b):
             L = w.seq_lens[b]
@@ -656,15 +599,22 @@ def main():
             vv = v_cache[idx].reshape(-1, hk, D)[:L].float().cpu()
             return kk, vv
 
-        s, tok, done = cpu_attention_sample(w, q_cpu, rows, args.cpu_seconds, order)
+        sample, tok = pick_sample(w, args.cpu_seconds, attend, q_cpu, rows)
+        s = time_sample(sample, attend, q_cpu)
         est = s * w.total_tokens / tok
-        line["cpu_baseline"] = {"value": est * 1e6, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                                "sample": f"{done} of {B} requests ({tok} of {w.total_tokens} context tokens), "
-                                          f"{s:.1f} s of dense fp32 attention, scaled by token count"}
+        line["cpu_baseline"] = {"value": est * 1e6, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+                                "extrapolated": tok < w.total_tokens,
+                                "sample": f"{len(sample)} of {B} requests ({tok} of {w.total_tokens} context tokens, the "
+                                          f"GPU's own K/V values), {s:.1f} s of dense fp32 attention, scaled by token count"}
+        ref_ms = reference_scheduler_ms(w, w.group, hk, 5)
+        if ref_ms is not None:
+            line["plan_build_ms"]["reference_cpp_scheduler_tree_and_pack"] = ref_ms
     print(json.dumps(line))
     if n > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not parity["ok"]:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -163,7 +163,6 @@ const int32_t* pat_work_blob(const pat_work* w, size_t* words);
  * ------------------------------------------------------------------------- */
 enum { PAT_DTYPE_FP16 = 0, PAT_DTYPE_BF16 = 1 };
 enum { PAT_SKIP_STREAM = 1, PAT_SKIP_DENSE = 2, PAT_SKIP_MERGE = 4,
-       PAT_DENSE_MMA_SYNC = 8, /* run the dense tiles on the legacy mma.sync kernel instead of tcgen05 */
        PAT_NO_OVERLAP = 16     /* do not let the streaming kernel start while the dense kernel runs */ };
 
 typedef struct pat_decode_args {
@@ -190,8 +189,14 @@ typedef struct pat_decode_args {
     /* scratch for the per-(item, query, KV head) partial results; 32-byte aligned */
     void* workspace;
     size_t workspace_bytes;
-    /* optional device int32[4]: [0] != 0 after the call means a bounded wait gave up */
+    /* Optional device int32[4].  It must hold zeros when the call starts (the library does not
+     * clear it: a non-zero word makes the dense kernel's CTAs return at once, as they do after a
+     * failure inside the same call).  [0] != 0 after the call means that a bounded wait inside a
+     * kernel gave up and `out` is not valid. */
     int32_t* status_word;
+    /* limit of every wait inside the kernels, in microseconds; 0 = one second */
+    int32_t wait_limit_us;
+    int32_t reserved;
 } pat_decode_args;
 
 size_t pat_b200_workspace_bytes(const pat_work_header* work, int num_q_heads, int head_dim);
@@ -221,6 +226,13 @@ int pat_b200_last_launch_count(void);
 #define PAT_B200_STATIC_SCRATCH_BYTES (32u << 20)
 int pat_b200_decode_static_scratch(const pat_decode_args* args, void* stream);
 
+/* Self-test of the kernels' bounded waits (no counterpart in the reference, whose kernels wait
+ * without a limit): launches one thread that waits on a barrier nobody arrives on, with nothing
+ * asynchronous in flight.  After the stream has drained, status_word[0] == 99 says that the wait
+ * gave up and the kernel returned, status_word[1] holds the nanoseconds it waited.
+ * limit_us in (0, 1 000 000]. */
+int pat_b200_selftest_wait(int32_t limit_us, int32_t* status_word, void* stream);
+
 /* ------------------------------------------------------------------------- *
  * KV-cache append: the step right before decode attention.
  * Replaces vLLM's reshape_and_cache_flash as called from the reference's serving backend
@@ -246,6 +258,17 @@ typedef struct pat_append_args {
 } pat_append_args;
 
 int pat_b200_append_kv(const pat_append_args* args, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * KV-head sharding: head order after the optional all-gather of the outputs.
+ * The reference has no multi-GPU path of its own (a tensor-parallel vLLM hands its backend
+ * per-rank head counts, plugin/vllm/attention/backends/prefix_attn.py:617-618, and never gathers).
+ * staged: what an all-gather of the ranks' [batch, 1, heads_per_rank, head_dim] outputs returns,
+ * [world][batch][heads_per_rank][head_dim]; full: [batch][1][world * heads_per_rank][head_dim],
+ * heads in rank order.  16-bit elements, 16-byte aligned buffers.
+ * ------------------------------------------------------------------------- */
+int pat_b200_reorder_heads(const void* staged, void* full, int world, int batch, int heads_per_rank,
+                           int head_dim, void* stream);
 
 #ifdef __cplusplus
 }

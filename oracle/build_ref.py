@@ -18,7 +18,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libpat_ref_tree.so")
-REFERENCE_ROOT = os.environ.get("PAT_REFERENCE_ROOT", "/root/reference")
+# The reference checkout: PAT_REFERENCE_ROOT, else a directory named "reference" beside this repository.
+REFERENCE_ROOT = os.environ.get("PAT_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def reference_header() -> str:

@@ -16,7 +16,9 @@ import os
 import sys
 import types
 
-REFERENCE_ROOT = os.environ.get("PAT_REFERENCE_ROOT", "/root/reference")
+# The reference checkout: PAT_REFERENCE_ROOT, else a directory named "reference" beside this repository.
+REFERENCE_ROOT = os.environ.get("PAT_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 _PKG = "_pat_reference_pkg"
 
 

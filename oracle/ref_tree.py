@@ -88,3 +88,16 @@ def run(block_size: int, seq_lens: Sequence[int], padded_table: np.ndarray,
         return out
     finally:
         lib.ref_tree_destroy(t)
+
+
+def time_pack(seq_lens: np.ndarray, padded_table: np.ndarray, block_size: int, hratio: int, kv_heads: int) -> None:
+    """One build + pack of the reference scheduler with the result left unread (for timing it)."""
+    lib = _lib()
+    lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    table = np.ascontiguousarray(padded_table, dtype=np.int32)
+    t = lib.ref_tree_create(block_size)
+    try:
+        lib.ref_tree_build(t, lens.ctypes.data, table.ctypes.data, table.shape[0], table.shape[1])
+        lib.ref_tree_pack(t, None, 0, hratio, kv_heads)
+    finally:
+        lib.ref_tree_destroy(t)

@@ -58,7 +58,7 @@ class DecodeArgs(C.Structure):
                 ("num_pages", C.c_int64), ("softmax_scale", C.c_float), ("flags", C.c_int32),
                 ("work_blob", C.c_void_p), ("work", WorkHeader),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("status_word", C.c_void_p)]
+                ("status_word", C.c_void_p), ("wait_limit_us", C.c_int32), ("reserved", C.c_int32)]
 
 
 class AppendArgs(C.Structure):
@@ -102,6 +102,8 @@ SIGNATURES = {
     "pat_b200_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "pat_b200_last_launch_count": (C.c_int, []),
     "pat_b200_decode_static_scratch": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "pat_b200_selftest_wait": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p]),
+    "pat_b200_reorder_heads": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "pat_b200_append_kv": (C.c_int, [C.POINTER(AppendArgs), C.c_void_p]),
 }
 STATIC_SCRATCH_BYTES = 32 << 20

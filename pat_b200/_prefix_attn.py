@@ -18,7 +18,8 @@ import torch
 from . import _native as N
 from . import _plan_cache
 
-__all__ = ["prefix_attn_with_kvcache", "PrefixTreeCPP", "KernelInfo", "WorkConfig", "DeviceWork"]
+__all__ = ["prefix_attn_with_kvcache", "PrefixTreeCPP", "KernelInfo", "WorkConfig", "DeviceWork",
+           "status_word", "check_status"]
 
 
 # --------------------------------------------------------------------------- options
@@ -87,10 +88,45 @@ class DeviceWork:
         host = torch.empty(words.value, dtype=torch.int32, pin_memory=device.type == "cuda")
         if words.value:
             C.memmove(host.data_ptr(), ptr, words.value * 4)
-        self._host = host                       # kept alive until the async copy is done
+        self._host = host                       # kept alive: the copy below is asynchronous
         self.blob = host.to(device, non_blocking=True)
         self.device = device
+        # The copy runs on the stream that is current in THIS thread (a plan-building worker thread
+        # uses the default stream); the kernels may be launched on another one.  The event lets the
+        # first launch on a different stream wait for the upload.
+        self._uploaded = None
+        self._upload_stream = None
+        if device.type == "cuda":
+            st = torch.cuda.current_stream(device)
+            self._uploaded = torch.cuda.Event()
+            self._uploaded.record(st)
+            self._upload_stream = st.cuda_stream
+        self._ordered = set()                   # streams already ordered after the upload
+        self._scratch = {}                      # (stream, bytes) -> workspace tensor
+        self._args = None                       # (key, DecodeArgs) of the last call
         lib.pat_work_destroy(handle)
+
+    def order_after_upload(self, stream) -> None:
+        """Makes ``stream`` wait for the upload of the blob (once per stream)."""
+        h = stream.cuda_stream
+        if self._uploaded is None or h == self._upload_stream or h in self._ordered:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            # an event recorded outside a capture cannot be waited for inside it: settle it on the host
+            self._uploaded.synchronize()
+        else:
+            stream.wait_event(self._uploaded)
+        self._ordered.add(h)
+
+    def workspace(self, nbytes: int, stream, device) -> torch.Tensor:
+        """Scratch for the partial results, reused by every call with this work list on ``stream``
+        (calls on one stream run one after the other, so they can share it)."""
+        key = (stream.cuda_stream, nbytes)
+        ws = self._scratch.get(key)
+        if ws is None:
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            self._scratch[key] = ws
+        return ws
 
     @classmethod
     def from_host_plan(cls, plan: "_plan_cache.HostPlan", hratio: int, kv_heads: int, page_size: int,
@@ -195,6 +231,7 @@ class KernelInfo:
         self.num_split_per_seq = move(self.num_split_per_seq)
         if device.type == "cuda":
             self.device_work(device)
+            check_status(device, synchronize=False)     # a failed wait of an earlier step surfaces here
 
     def device_work(self, device: torch.device, cfg: Optional[WorkConfig] = None) -> DeviceWork:
         cfg = cfg or default_config()
@@ -333,30 +370,96 @@ def _check_index(t: torch.Tensor, name: str, shape=None):
         _check(tuple(t.shape) == tuple(shape), f"{name} must have shape {tuple(shape)}")
 
 
-def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None, status=None, flags=0):
+_status_words = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32[4] the kernels report a failed bounded wait in (zero = fine)."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    t = _status_words.get(device)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_words[device] = t
+    return t
+
+
+def check_status(device=None, synchronize: bool = True) -> None:
+    """Raises if a kernel of an earlier call on ``device`` gave up on a bounded wait (its output is
+    then not valid).  With ``synchronize=False`` the word is read on a side stream without waiting
+    for queued work, which is how a plan build checks it in passing."""
+    devices = [torch.device(device)] if device is not None else list(_status_words)
+    for dev in devices:
+        t = _status_words.get(dev if dev.index is not None else torch.device("cuda", torch.cuda.current_device()))
+        if t is None:
+            continue
+        if synchronize:
+            code = int(t[0].item())
+        else:
+            side = _side_stream(t.device)
+            with torch.cuda.stream(side):
+                code = int(t[0].item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(f"a decode-attention kernel gave up on a bounded wait (code {code}); "
+                               "outputs since the last check are not valid")
+
+
+_side_streams = {}
+
+
+def _side_stream(device):
+    s = _side_streams.get(device)
+    if s is None:
+        s = torch.cuda.Stream(device)
+        _side_streams[device] = s
+    return s
+
+
+def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None, status=None, flags=0,
+         wait_limit_us=0):
     lib = N.load()
-    B, _, H, D = q.shape
-    a = N.DecodeArgs()
-    a.q, a.k_cache, a.v_cache, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
-    a.lse_out = lse_out.data_ptr() if lse_out is not None else None
-    a.q_batch_stride, a.q_head_stride = q.stride(0), q.stride(2)
-    a.k_page_stride, a.k_row_stride, a.k_head_stride = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
-    a.v_page_stride, a.v_row_stride, a.v_head_stride = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
-    a.out_batch_stride, a.out_head_stride = out.stride(0), out.stride(2)
-    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = B, H, k_cache.shape[2], D
-    a.page_size = k_cache.shape[1]
-    a.dtype = _DTYPES[q.dtype]
-    a.num_pages = k_cache.shape[0]
-    a.softmax_scale = float(scale)
-    a.flags = int(flags)
-    a.work_blob = work.blob.data_ptr()
-    a.work = work.header
-    need = lib.pat_b200_workspace_bytes(C.byref(work.header), H, D)
-    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
-    a.workspace, a.workspace_bytes = ws.data_ptr(), need
-    a.status_word = status.data_ptr() if status is not None else None
-    stream = torch.cuda.current_stream(q.device).cuda_stream
-    rc = lib.pat_b200_decode(C.byref(a), C.c_void_p(stream))
+    stream = torch.cuda.current_stream(q.device)
+    work.order_after_upload(stream)
+    if status is None:
+        status = status_word(q.device)
+    key = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+           lse_out.data_ptr() if lse_out is not None else 0, status.data_ptr(), stream.cuda_stream,
+           q.shape, q.stride(), k_cache.shape, k_cache.stride(), v_cache.stride(), out.stride(),
+           q.dtype, float(scale), int(flags), int(wait_limit_us))
+    # Inside a stream capture the scratch must come from the graph's own memory pool (it has to
+    # live as long as the graph, not as long as this work list), so nothing is cached there.
+    capturing = torch.cuda.is_current_stream_capturing()
+    cached = work._args
+    if cached is not None and cached[0] == key and not capturing:
+        a = cached[1]
+    else:
+        B, _, H, D = q.shape
+        a = N.DecodeArgs()
+        a.q, a.k_cache, a.v_cache, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+        a.lse_out = lse_out.data_ptr() if lse_out is not None else None
+        a.q_batch_stride, a.q_head_stride = q.stride(0), q.stride(2)
+        a.k_page_stride, a.k_row_stride, a.k_head_stride = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+        a.v_page_stride, a.v_row_stride, a.v_head_stride = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
+        a.out_batch_stride, a.out_head_stride = out.stride(0), out.stride(2)
+        a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = B, H, k_cache.shape[2], D
+        a.page_size = k_cache.shape[1]
+        a.dtype = _DTYPES[q.dtype]
+        a.num_pages = k_cache.shape[0]
+        a.softmax_scale = float(scale)
+        a.flags = int(flags)
+        a.work_blob = work.blob.data_ptr()
+        a.work = work.header
+        need = lib.pat_b200_workspace_bytes(C.byref(work.header), H, D)
+        ws = (torch.empty(need, dtype=torch.uint8, device=q.device) if capturing
+              else work.workspace(need, stream, q.device))
+        a.workspace, a.workspace_bytes = ws.data_ptr(), need
+        a.status_word = status.data_ptr()
+        a.wait_limit_us = int(wait_limit_us)
+        if not capturing:
+            work._args = (key, a)
+    rc = lib.pat_b200_decode(C.byref(a), C.c_void_p(stream.cuda_stream))
     if rc != 0:
         raise RuntimeError(f"prefix_attn_with_kvcache failed: {N.strerror(rc)} ({rc})")
 
@@ -381,6 +484,7 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
     lse_out = kwargs.pop("lse_out", None)
     status = kwargs.pop("_status", None)
     flags = kwargs.pop("_flags", 0)
+    wait_limit_us = kwargs.pop("_wait_limit_us", 0)
     names16 = ["q", "k_cache_paged", "v_cache_paged", "num_split_per_seq", "query_tables", "block_tables",
                "num_seqs_per_CTAs", "CTA_ranks", "kv_in_CTAs", "MNW", "max_split_per_seq", "max_seqs_in_CTA",
                "max_blocks_in_CTA", "softmax_scale", "out", "timing_"]
@@ -476,7 +580,7 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
             tag.work[key] = work
 
     with torch.cuda.device(q.device):
-        _run(q, k_cache, v_cache, work, scale, out, lse_out, status, flags)
+        _run(q, k_cache, v_cache, work, scale, out, lse_out, status, flags, wait_limit_us)
 
 
 def last_launch_count() -> int:

@@ -18,7 +18,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libpat_b200.so")
-SOURCES = ["pat_tree.cpp", "pat_work.cpp", "pat_capi.cpp", "pat_decode.cu", "pat_append.cu"]
+SOURCES = ["pat_tree.cpp", "pat_work.cpp", "pat_capi.cpp", "pat_decode.cu", "pat_append.cu", "pat_gather.cu"]
 HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))) + [
     os.path.join("..", "..", "include", "pat_b200.h")]
 

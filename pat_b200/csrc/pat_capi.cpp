@@ -58,7 +58,7 @@ void copy_header(const pat::WorkHeader& h, pat_work_header* out) {
 
 extern "C" {
 
-int pat_b200_abi_version(void) { return 2; }
+int pat_b200_abi_version(void) { return 3; }
 
 const char* pat_b200_strerror(int status) {
     switch (status) {

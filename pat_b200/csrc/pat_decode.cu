@@ -37,8 +37,28 @@ EncodeFn get_encode_fn() {
 
 // View of a paged cache [pages, page_size, kv_heads, D] as a 4-D tensor
 // (D, kv_heads, page_size, pages) with a [64, 1, 16, 1] box and 128-byte swizzle.
+// A decode loop calls with the same two caches step after step, so the last few encoded maps are
+// kept per host thread (a map depends only on the values in its key).
+struct MapKey {
+    const void* base;
+    int dt, head_dim, kv_heads, page_size;
+    int64_t pages, head_stride, row_stride, page_stride;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && dt == o.dt && head_dim == o.head_dim && kv_heads == o.kv_heads &&
+               page_size == o.page_size && pages == o.pages && head_stride == o.head_stride &&
+               row_stride == o.row_stride && page_stride == o.page_stride;
+    }
+};
+constexpr int kMapCache = 4;
+struct MapCacheEntry { MapKey key; CUtensorMap map; bool valid; };
+thread_local MapCacheEntry g_map_cache[kMapCache];
+thread_local int g_map_next = 0;
+
 int make_cache_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int head_dim, int kv_heads,
                    int page_size, int64_t pages, int64_t head_stride, int64_t row_stride, int64_t page_stride) {
+    const MapKey key{base, static_cast<int>(dt), head_dim, kv_heads, page_size, pages, head_stride, row_stride, page_stride};
+    for (const MapCacheEntry& e : g_map_cache)
+        if (e.valid && e.key == key) { *map = e.map; return PAT_OK; }
     EncodeFn enc = get_encode_fn();
     if (!enc) return PAT_ERR_CUDA;
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(kv_heads),
@@ -50,7 +70,13 @@ int make_cache_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, i
     const CUresult rc = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return rc == CUDA_SUCCESS ? PAT_OK : PAT_ERR_CUDA;
+    if (rc != CUDA_SUCCESS) return PAT_ERR_CUDA;
+    MapCacheEntry& slot = g_map_cache[g_map_next];
+    g_map_next = (g_map_next + 1) % kMapCache;
+    slot.key = key;
+    slot.map = *map;
+    slot.valid = true;
+    return PAT_OK;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -88,11 +114,11 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     p.scale = a.softmax_scale;
     p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
     p.status = a.status_word;
+    p.wait_ns = a.wait_limit_us > 0 ? static_cast<uint64_t>(a.wait_limit_us) * 1000ull : kDefaultWaitNs;
 
     int launches = 0;
     const bool streaming = a.work.num_stream_items > 0 && !(a.flags & PAT_SKIP_STREAM);
     const bool dense = a.work.num_dense_items > 0 && !(a.flags & PAT_SKIP_DENSE);
-    const bool dense_tc = dense && !(a.flags & PAT_DENSE_MMA_SYNC);
 
     // The streaming kernel is bound by HBM, the dense kernel by the tensor and special-function
     // units of the SMs it holds, and it needs few of them when the work list sized it so
@@ -101,8 +127,8 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     // running (each signals that at its top; the streaming kernel never waits for the dense
     // kernel's results), fills the SMs the dense kernel leaves and takes the others over as the
     // dense CTAs retire.  The merge kernel is an ordinary launch and waits for both.
-    const bool overlap = streaming && dense_tc && !(a.flags & PAT_NO_OVERLAP);
-    if (dense_tc) {
+    const bool overlap = streaming && dense && !(a.flags & PAT_NO_OVERLAP);
+    if (dense) {
         // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
         static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
         auto kern = dense_tc_kernel<T, D>;
@@ -145,22 +171,6 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         cfg.attrs = &attr;
         cfg.numAttrs = overlap ? 1 : 0;
         if (cudaLaunchKernelEx(&cfg, kern, p, kmap, vmap) != cudaSuccess) return PAT_ERR_CUDA;
-        ++launches;
-    }
-    if (dense && !dense_tc) {
-        // the same items on the legacy mma.sync path (kept for comparison): one CTA per
-        // (item, 128-row half)
-        static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
-        auto kern = dense_kernel<T, D>;
-        constexpr int smem = dense_smem_bytes<D>();
-        if (!configured[dev].load(std::memory_order_acquire)) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                return PAT_ERR_CUDA;
-            configured[dev].store(true, std::memory_order_release);
-        }
-        p.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
-        p.num_items = a.work.num_dense_items;
-        kern<<<dim3(static_cast<unsigned>(a.work.num_dense_items), 2), (kDenseWarps + 1) * 32, smem, stream>>>(p, kmap, vmap);
         ++launches;
     }
     if (!(a.flags & PAT_SKIP_MERGE)) {
@@ -283,4 +293,31 @@ extern "C" int pat_b200_decode_static_scratch(const pat_decode_args* args, void*
     local.workspace = ptr;
     local.workspace_bytes = PAT_B200_STATIC_SCRATCH_BYTES;
     return pat_b200_decode(&local, stream_handle);
+}
+
+// ------------------------------------------------------------------------------
+// Self-test of the bounded wait
+// ------------------------------------------------------------------------------
+namespace {
+// One thread waits on an mbarrier that nobody ever arrives on, with nothing asynchronous in
+// flight: the wait must run out after `limit_ns`, report through the status word and return.
+__global__ void selftest_wait_kernel(int32_t* status, uint64_t limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        pat::mbar_init(pat::smem_u32(&bar), 1);
+        pat::mbar_fence_init();
+        const uint64_t t0 = pat::global_timer_ns();
+        const bool ok = pat::mbar_wait(pat::smem_u32(&bar), 0, limit_ns);
+        const uint64_t waited = pat::global_timer_ns() - t0;
+        status[0] = ok ? 0 : 99;
+        status[1] = static_cast<int32_t>(waited > 0x7fffffffull ? 0x7fffffffull : waited);
+    }
+}
+}  // namespace
+
+extern "C" int pat_b200_selftest_wait(int32_t limit_us, int32_t* status_word, void* stream_handle) {
+    if (!status_word || limit_us <= 0 || limit_us > 1000000) return PAT_ERR_BAD_ARGUMENT;
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_handle)>>>(
+        status_word, static_cast<uint64_t>(limit_us) * 1000ull);
+    return cudaGetLastError() == cudaSuccess ? PAT_OK : PAT_ERR_CUDA;
 }

@@ -33,8 +33,10 @@
 // as TMEM allows (N = 128 tokens for Q K^T).
 // The running maximum is only raised when a tile exceeds it by more than 2^8 (the offset
 // cancels in O / l), so the O accumulator in TMEM is rescaled rarely.
-// Every mbarrier wait is bounded; a wait that gives up records a code in the status word,
-// later waits are skipped and the CTA still frees its TMEM before it returns.
+// Every mbarrier wait is bounded.  A wait that gives up records a code in the status word; the
+// role that gave up issues nothing more (no TMA request, no MMA), waits briefly for what it had
+// in flight, the other roles' waits then run out too, and all eleven warps meet at one barrier
+// before the CTA frees its TMEM and returns.
 #pragma once
 
 #include "pat_kernels.cuh"
@@ -221,12 +223,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     const uint32_t sQ = base + L::kQOff, sK = base + L::kKOff, sV = base + L::kVOff;
     const uint32_t bars = base + L::kBarOff;
     // barrier map (8 bytes each): full_k[R] empty_k[R] full_v[R] empty_v[R] s_full[R] p_ready[R]
-    // o_done[R] q_ready o_free
+    // o_done[R] q_ready o_free drain
     const uint32_t bar_full_k = bars, bar_empty_k = bars + 8 * R, bar_full_v = bars + 16 * R, bar_empty_v = bars + 24 * R,
                    bar_s = bars + 32 * R, bar_p = bars + 40 * R, bar_o = bars + 48 * R, bar_q = bars + 56 * R,
-                   bar_ofree = bars + 56 * R + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 56 * R + 16);
-    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 56 * R + 24);
+                   bar_ofree = bars + 56 * R + 8, bar_drain = bars + 56 * R + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tc_smem + L::kBarOff + 56 * R + 24);
+    volatile int* poisoned = reinterpret_cast<volatile int*>(tc_smem + L::kBarOff + 56 * R + 32);
     float* xch = reinterpret_cast<float*>(tc_smem + L::kXchOff);      // [2][2][128]
 
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
@@ -245,6 +247,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         for (int i = 0; i < R; ++i) mbar_init(bar_o + 8 * i, 1);                // o_done
         mbar_init(bar_q, kSW * 32);                                             // q_ready
         mbar_init(bar_ofree, kSW * 32);                                         // o_free
+        mbar_init(bar_drain, 1);                                                // only used when a wait gave up
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTcTmemCols);
@@ -272,7 +275,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
             const int32_t* item_pages = p.pages + page_off;
             for (int j = 0; j < n_tiles; ++j, ++t) {
-                if (t >= R) ok = mbar_wait(empty + 8 * s, ph);
+                if (t >= R) ok = mbar_wait(empty + 8 * s, ph, p.wait_ns);
                 if (!ok) break;
                 constexpr int kSub = kTcTile / 16;
                 const int subs = min(kSub, n_sub - j * kSub);
@@ -291,11 +294,14 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 if (++s == R) { s = 0; ph ^= 1; }
             }
         }
-        if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
-        return;
-    }
-
-    if (warp == kSW + 1) {
+        if (!ok) {
+            // Gave up: nothing more is requested.  The last R tiles requested may still be on their
+            // way into the ring; give each a short second wait so that none lands after the CTA
+            // has handed its shared memory back.
+            if (lane == 0 && p.status) atomicExch(p.status, 11);
+            for (int tt = max(0, t - R); tt < t; ++tt) mbar_wait(full + 8 * (tt % R), (tt / R) & 1, kDrainWaitNs);
+        }
+    } else if (warp == kSW + 1) {
         // ---- MMA issuer (one thread) -------------------------------------------------------------
         // The issuing thread is the narrowest resource of the CTA, so every descriptor is reduced
         // to "base word + slot * stride + constant": the high words are constants, the low words
@@ -338,11 +344,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         // S(tile at the cursor) = Q K^T into ring slot `slot`; on its own (not interleaved)
         auto qk_alone = [&](int slot, uint32_t phase) {
             if (qk_j == 0) {            // a new item: its Q rows must be in shared memory
-                if (ok) ok = mbar_wait(bar_q, qk_items & 1);
+                if (ok) ok = mbar_wait(bar_q, qk_items & 1, p.wait_ns);
                 ++qk_items;
             }
-            if (ok) ok = mbar_wait(bar_full_k + 8 * slot, phase);
+            if (ok) ok = mbar_wait(bar_full_k + 8 * slot, phase, p.wait_ns);
             ok = __all_sync(kFullMask, ok);
+            if (!ok) return;            // gave up: nothing more is issued
             tc_fence_after();
             {
                 uint32_t q_w = q_lo, k_w = k_lo0 + slot * kSlotStep, acc = 0;
@@ -362,19 +369,20 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         int s = 0;                              // ring slot and phase of tile g
         uint32_t ph = 0;
         qk_alone(0, 0);
-        if (total_tiles > 1) qk_alone(1, 0);
-        for (int g = 0; g < total_tiles; ++g) {
+        if (ok && total_tiles > 1) qk_alone(1, 0);
+        for (int g = 0; g < total_tiles && ok; ++g) {
             const bool have_a = g + 2 < total_tiles;
             const bool a_new_item = have_a && qk_j == 0;       // S(g + 2) opens an item: issued after P V(g)
             const bool qk = have_a && !a_new_item;
             const int sa = slot_add(s, 2);
             const uint32_t pha = sa < s ? ph ^ 1 : ph;
-            if (qk && ok) ok = mbar_wait(bar_full_k + 8 * sa, pha);
-            if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
-            if (ok) ok = mbar_wait(bar_p + 8 * s, ph);             // P(g) is in TMEM (over S(g))
+            if (qk && ok) ok = mbar_wait(bar_full_k + 8 * sa, pha, p.wait_ns);
+            if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph, p.wait_ns);
+            if (ok) ok = mbar_wait(bar_p + 8 * s, ph, p.wait_ns);  // P(g) is in TMEM (over S(g))
             if (pv_j == 0 && pv_items > 0 && ok)
-                ok = mbar_wait(bar_ofree, (pv_items - 1) & 1);     // the softmax warps have read the previous item's O
+                ok = mbar_wait(bar_ofree, (pv_items - 1) & 1, p.wait_ns);   // the softmax warps have read the previous item's O
             ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
+            if (!ok) break;                     // gave up: nothing more is issued
             tc_fence_after();
             // slot sa held tile g - 1, whose P V was issued in the previous iteration; MMAs execute in
             // issue order, so S(g + 2) may overwrite it now
@@ -409,10 +417,15 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                                                 // write once they have seen the last S of this item
             if (++s == R) { s = 0; ph ^= 1; }
         }
-        if (!ok && lane == 0 && p.status) atomicExch(p.status, 13);
-        return;
-    }
-
+        if (!ok) {
+            // Products issued before the wait that gave up may still be running: one last commit
+            // arrives on the drain barrier when all of them have completed, and the warp waits for
+            // that (bounded) before the CTA frees its tensor memory.
+            if (lane == 0 && p.status) atomicExch(p.status, 13);
+            if (elect_one()) tc_commit(bar_drain);
+            mbar_wait(bar_drain, 0, p.wait_ns);
+        }
+    } else {
     // ---- softmax warps ---------------------------------------------------------------------------
     // Thread (half, quad, lane) owns row r = 32 quad + lane (TMEM lane r) and the token columns
     // [32 half, 32 half + 32) of every tile; the two threads of a row exchange their maxima through
@@ -431,7 +444,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     uint32_t o_ph = 0;
     auto ensure_o = [&](int upto) {             // every o_done phase is consumed exactly once, in order
         while (o_seen < upto) {
-            if (ok) ok = mbar_wait(bar_o + 8 * o_slot, o_ph);
+            if (ok) ok = mbar_wait(bar_o + 8 * o_slot, o_ph, p.wait_ns);
             ++o_seen;
             if (++o_slot == R) { o_slot = 0; o_ph ^= 1; }
         }
@@ -489,13 +502,13 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 // that item's first S tiles while this item is still being finished.
                 uint4 qv[D / 16];
                 q_fetch(q_next, qv);            // in flight during the wait
-                if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
+                if (ok) ok = mbar_wait(bar_s + 8 * s, ph, p.wait_ns);
                 tc_fence_after();
                 q_store(qv);
                 tc_fence_before();
                 mbar_arrive(bar_q);
             } else {
-                if (ok) ok = mbar_wait(bar_s + 8 * s, ph);
+                if (ok) ok = mbar_wait(bar_s + 8 * s, ph, p.wait_ns);
                 tc_fence_after();
             }
             constexpr int CH = kTcTile / 2;     // token columns per thread
@@ -549,7 +562,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             if (valid < kTcTile) {
                 // V rows past the valid tokens may hold anything (stale tiles, never written pages):
                 // zero them (once the tile's V has landed) so that P = 0 times garbage cannot make a NaN
-                if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph);
+                if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph, p.wait_ns);
                 const int rows = kTcTile - valid;
                 const int chunks = rows * 8 * L::kBoxes;
                 for (int i = tid; i < chunks; i += kSW * 32) {
@@ -607,8 +620,12 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         }
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
+    }
+    // Every warp of the CTA ends here, also after a wait that gave up (the producers and the MMA
+    // warp have then waited for what they had in flight), so tensor memory and shared memory are
+    // only handed back once nothing can still write to them.
     tc_fence_before();
-    named_bar_sync(1, kSW * 32);
+    __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, kTcTmemCols);
 }
 

@@ -48,23 +48,27 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: false if the phase did not complete within about kMaxWaitNs (or kMaxPolls
-// polls, whichever comes first).  The clock is only read every 256 polls.
-constexpr uint64_t kMaxWaitNs = 1000ull * 1000ull * 1000ull;
+// Bounded wait: false if the phase did not complete within about `limit_ns` (or kMaxPolls
+// polls, whichever comes first).  The clock is only read every 64 polls.  Kernels take the limit
+// as a parameter (kDefaultWaitNs unless the caller asks otherwise).
+constexpr uint64_t kDefaultWaitNs = 1000ull * 1000ull * 1000ull;
 // The polling loop is kept out of line: a kernel waits in many places, and warps that run a
 // little code per tile (TMA producers, the MMA issuer) are bound by instruction fetch.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
     const uint64_t start = global_timer_ns();
     for (uint32_t i = 1; i < kMaxPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0 && global_timer_ns() - start > kMaxWaitNs) return false;
+        if ((i & 63u) == 0 && global_timer_ns() - start > limit_ns) return false;
     }
     return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity);
+    return mbar_wait_slow(bar, parity, limit_ns);
 }
+// After a wait has given up: a short second chance (about 20 us) for copies or products that
+// are still on their way, so that nothing lands in memory the CTA has already handed back.
+constexpr uint64_t kDrainWaitNs = 20ull * 1000ull;
 
 // ---- TMA: 4-D tiled load of one [16 tokens x 64 elements] box -----------------
 // coordinates: (element within head, kv head, row within page, page)

@@ -10,10 +10,7 @@
 //                   share of the item's 16-token sub-tiles - no CTA-wide barrier
 //                   in the main loop - and the warps' partial softmax states are
 //                   combined through shared memory at the end.
-//   dense_kernel  : up to 128 query rows sharing one KV segment.  A producer warp
-//                   streams 64-token K/V stages by TMA; eight consumer warps own
-//                   16 rows each and read every staged tile once from shared
-//                   memory, so a shared page is fetched once per 128 rows.
+//   (segments that many queries share run in dense_tc_kernel, pat_dense_tc.cuh)
 //   merge_kernel  : one warp per (request, head): out = sum_i e^(lse_i-lse) O_i.
 //
 // All kernels replace csrc/pat_fwd_kernel.h (pat_kernel :25-299, gather_kernel
@@ -41,20 +38,15 @@ struct AttnParams {
     float scale;          // softmax scale
     float scale_log2;     // scale * log2(e)
     int32_t* status;      // optional
+    uint64_t wait_ns;     // limit of every mbarrier wait
 };
 
 constexpr int kStreamWarps = 3;
 constexpr int kStreamStages = 3;
-constexpr int kDenseWarps = 8;          // consumer warps (16 rows each)
-constexpr int kDenseStages = 3;
-constexpr int kDenseSub = 4;            // 16-token sub-tiles per dense stage (64 tokens)
 constexpr int kScratchPad = 8;          // floats of padding per scratch row
 
 template <int D> constexpr int stream_smem_bytes() {
     return kStreamWarps * kStreamStages * TileGeom<D>::kSubBytes + 1024;
-}
-template <int D> constexpr int dense_smem_bytes() {
-    return kDenseStages * kDenseSub * TileGeom<D>::kSubBytes + 1024;
 }
 
 // Q rows of one 16-row tile straight into mma A fragments.
@@ -165,7 +157,14 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
 
     for (int j = 0; j < my_n; ++j) {
         const int s = j % S;
-        if (!mbar_wait(my_bar + s * 8, (j / S) & 1)) { ok = false; break; }
+        if (!mbar_wait(my_bar + s * 8, (j / S) & 1, p.wait_ns)) {
+            // Give up: no further load is issued.  Tiles j .. j + S - 1 may still be on their way
+            // into this warp's stages; give each a short second wait so that none lands after
+            // the CTA has gone.
+            ok = false;
+            for (int jj = j; jj < min(j + S, my_n); ++jj) mbar_wait(my_bar + (jj % S) * 8, (jj / S) & 1, kDrainWaitNs);
+            break;
+        }
         const int t = warp + j * W;
         const int valid = min(16, kv_len - (t << 4));
         if (valid < 16) {
@@ -195,185 +194,56 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
         sm_l[warp][(lane >> 2) + 8] = l[1];
     }
     __syncthreads();   // every warp is done with its pipeline memory
-    if (sm_abort) return;
-
-    constexpr int kRowStride = D + kScratchPad;
-    float* scratch = reinterpret_cast<float*>(smem);     // [W][16][D + pad]
-    {
-        const int r0 = lane >> 2, r1 = r0 + 8;
-        float g0 = -INFINITY, g1 = -INFINITY;
+    if (!sm_abort) {
+        constexpr int kRowStride = D + kScratchPad;
+        float* scratch = reinterpret_cast<float*>(smem);     // [W][16][D + pad]
+        {
+            const int r0 = lane >> 2, r1 = r0 + 8;
+            float g0 = -INFINITY, g1 = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < W; ++w) { g0 = fmaxf(g0, sm_m[w][r0]); g1 = fmaxf(g1, sm_m[w][r1]); }
-        const float f0 = (m[0] == -INFINITY) ? 0.f : fast_exp2((m[0] - g0) * p.scale_log2);
-        const float f1 = (m[1] == -INFINITY) ? 0.f : fast_exp2((m[1] - g1) * p.scale_log2);
-        float* base = scratch + static_cast<size_t>(warp) * 16 * kRowStride;
-        const int col = (lane & 3) << 1;
+            for (int w = 0; w < W; ++w) { g0 = fmaxf(g0, sm_m[w][r0]); g1 = fmaxf(g1, sm_m[w][r1]); }
+            const float f0 = (m[0] == -INFINITY) ? 0.f : fast_exp2((m[0] - g0) * p.scale_log2);
+            const float f1 = (m[1] == -INFINITY) ? 0.f : fast_exp2((m[1] - g1) * p.scale_log2);
+            float* base = scratch + static_cast<size_t>(warp) * 16 * kRowStride;
+            const int col = (lane & 3) << 1;
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            *reinterpret_cast<float2*>(base + r0 * kRowStride + i * 8 + col) = make_float2(o[i][0] * f0, o[i][1] * f0);
-            *reinterpret_cast<float2*>(base + r1 * kRowStride + i * 8 + col) = make_float2(o[i][2] * f1, o[i][3] * f1);
-        }
-    }
-    __syncthreads();
-
-    constexpr int kVec = D / 4;   // float4 per row
-    for (int idx = tid; idx < rows_valid * kVec; idx += W * 32) {
-        const int row = idx / kVec, v4 = idx - row * kVec;
-        float g = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < W; ++w) g = fmaxf(g, sm_m[w][row]);
-        float L = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int w = 0; w < W; ++w) {
-            const float mw = sm_m[w][row];
-            const float f = (mw == -INFINITY) ? 0.f : fast_exp2((mw - g) * p.scale_log2);
-            L += sm_l[w][row] * f;
-            const float4 x = *reinterpret_cast<const float4*>(scratch + (static_cast<size_t>(w) * 16 + row) * kRowStride + v4 * 4);
-            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
-        }
-        const float inv = 1.f / L;
-        const int qi = row / p.hratio, gg = row - qi * p.hratio;
-        // entry of (query qi, KV head kvh) = entry_base + qi * kv_heads + kvh; hratio rows per entry
-        const size_t slot = (static_cast<size_t>(entry_base) + static_cast<size_t>(qi) * p.kv_heads + kvh) * p.hratio + gg;
-        *reinterpret_cast<float4*>(p.part_o + slot * D + v4 * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-        if (v4 == 0) p.part_lse[slot] = g * p.scale + logf(L);
-    }
-}
-
-// ------------------------------------------------------------------------------
-// Dense kernel (mma.sync tiles; 8 consumer warps x 16 rows + 1 producer warp)
-// ------------------------------------------------------------------------------
-template <typename T, int D>
-__global__ void __launch_bounds__((kDenseWarps + 1) * 32)
-dense_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
-    using G = TileGeom<D>;
-    constexpr int W = kDenseWarps, S = kDenseStages, U = kDenseSub;
-    constexpr int kStageBytes = U * G::kSubBytes;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S];
-
-    // One dense item (<= 256 rows, its own KV head) per blockIdx.x; blockIdx.y picks the
-    // 128-row half this CTA computes.
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int32_t* it = p.items + static_cast<size_t>(blockIdx.x) * 8;
-    const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
-              entry_base = __ldg(it + 4), kvh = __ldg(it + 5);
-    const int rows_valid = nq * p.hratio;
-    const int half_base = blockIdx.y * (W * 16);
-    if (half_base >= rows_valid) return;
-
-    if (tid == 0) {
-        tma_prefetch_desc(&kmap);
-        tma_prefetch_desc(&vmap);
-        for (int i = 0; i < S; ++i) {
-            mbar_init(smem_u32(&full_bar[i]), 1);
-            mbar_init(smem_u32(&empty_bar[i]), W);
-        }
-        mbar_fence_init();
-    }
-    __syncthreads();
-
-    const int n_sub = (kv_len + 15) >> 4;           // 16-token sub-tiles
-    const int n_stage_tiles = (n_sub + U - 1) / U;  // 64-token stages
-    const int tiles_per_page = p.page_size >> 4;
-    const int32_t* item_pages = p.pages + page_off;
-    const uint32_t smem_addr = smem_u32(smem);
-
-    if (warp == W) {
-        // ---- producer warp ------------------------------------------------------
-        for (int j = 0; j < n_stage_tiles; ++j) {
-            const int s = j % S;
-            if (j >= S) {
-                if (!mbar_wait(smem_u32(&empty_bar[s]), ((j / S) - 1) & 1)) {
-                    if (lane == 0 && p.status) atomicExch(p.status, 2);
-                    return;
-                }
-            }
-            const int subs = min(U, n_sub - j * U);
-            // lanes 0..subs-1 each fetch one page id and issue the boxes of one sub-tile
-            if (lane == 0) mbar_expect_tx(smem_u32(&full_bar[s]), subs * G::kSubBytes);
-            __syncwarp();
-            if (lane < subs) {
-                const int t = j * U + lane;
-                const int page = __ldg(item_pages + t / tiles_per_page);
-                const int row0 = (t % tiles_per_page) << 4;
-                const uint32_t dst = smem_addr + s * kStageBytes + lane * G::kSubBytes;
-                const uint32_t bar = smem_u32(&full_bar[s]);
-#pragma unroll
-                for (int b = 0; b < G::kBoxes; ++b) {
-                    tma_load_4d(dst + b * 2048, &kmap, bar, b * 64, kvh, row0, page);
-                    tma_load_4d(dst + G::kOperandBytes + b * 2048, &vmap, bar, b * 64, kvh, row0, page);
-                }
-            }
-            __syncwarp();
-        }
-        return;
-    }
-
-    // ---- consumer warps -----------------------------------------------------------
-    const int row_base = half_base + warp * 16;
-    const bool active = row_base < rows_valid;   // warps without rows still release stages
-    uint32_t qf[D / 16][4];
-    load_q_frags<T, D>(qf, p, p.queries + q_off, row_base, rows_valid, kvh, lane);
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-
-    for (int j = 0; j < n_stage_tiles; ++j) {
-        const int s = j % S;
-        if (!mbar_wait(smem_u32(&full_bar[s]), (j / S) & 1)) {
-            if (lane == 0 && p.status) atomicExch(p.status, 3);
-            return;
-        }
-        const int subs = min(U, n_sub - j * U);
-        const int valid = min(16 * U, kv_len - j * 16 * U);
-        const uint32_t stage = smem_addr + s * kStageBytes;
-        if (active) {
-            if (subs == U) {
-                if (valid < 16 * U) {
-                    // only reached on the last stage: the tail sub-tile holds garbage rows
-                    // (each consumer zeroes its own view; same values, benign duplication)
-                    zero_v_tail<D>(smem + s * kStageBytes, U - 1, valid - 16 * (U - 1), lane);
-                    __syncwarp();
-                }
-                warp_attend_tile<T, D, U>(qf, o, m, l, stage, valid, p.scale_log2, lane);
-            } else {
-                for (int u = 0; u < subs; ++u) {
-                    const int v = min(16, valid - 16 * u);
-                    if (v < 16) {
-                        zero_v_tail<D>(smem + s * kStageBytes, u, v, lane);
-                        __syncwarp();
-                    }
-                    warp_attend_tile<T, D, 1>(qf, o, m, l, stage + u * G::kSubBytes, v, p.scale_log2, lane);
-                }
+            for (int i = 0; i < D / 8; ++i) {
+                *reinterpret_cast<float2*>(base + r0 * kRowStride + i * 8 + col) = make_float2(o[i][0] * f0, o[i][1] * f0);
+                *reinterpret_cast<float2*>(base + r1 * kRowStride + i * 8 + col) = make_float2(o[i][2] * f1, o[i][3] * f1);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
-    }
+        __syncthreads();
 
-    if (!active) return;
-    l[0] += __shfl_xor_sync(kFullMask, l[0], 1);
-    l[0] += __shfl_xor_sync(kFullMask, l[0], 2);
-    l[1] += __shfl_xor_sync(kFullMask, l[1], 1);
-    l[1] += __shfl_xor_sync(kFullMask, l[1], 2);
-    const int col = (lane & 3) << 1;
+        constexpr int kVec = D / 4;   // float4 per row
+        for (int idx = tid; idx < rows_valid * kVec; idx += W * 32) {
+            const int row = idx / kVec, v4 = idx - row * kVec;
+            float g = -INFINITY;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int row = row_base + (lane >> 2) + 8 * h;
-        if (row >= rows_valid) continue;
-        const int qi = row / p.hratio, gg = row - qi * p.hratio;
-        const size_t slot = static_cast<size_t>(entry_base + qi) * p.hratio + gg;   // dense entries are per KV head
-        const float inv = 1.f / l[h];
-        float* dst = p.part_o + slot * D + col;
+            for (int w = 0; w < W; ++w) g = fmaxf(g, sm_m[w][row]);
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i)
-            *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-        if ((lane & 3) == 0) p.part_lse[slot] = m[h] * p.scale + logf(l[h]);
+            for (int w = 0; w < W; ++w) {
+                const float mw = sm_m[w][row];
+                const float f = (mw == -INFINITY) ? 0.f : fast_exp2((mw - g) * p.scale_log2);
+                L += sm_l[w][row] * f;
+                const float4 x = *reinterpret_cast<const float4*>(scratch + (static_cast<size_t>(w) * 16 + row) * kRowStride + v4 * 4);
+                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+            }
+            const float inv = 1.f / L;
+            const int qi = row / p.hratio, gg = row - qi * p.hratio;
+            // entry of (query qi, KV head kvh) = entry_base + qi * kv_heads + kvh; hratio rows per entry
+            const size_t slot = (static_cast<size_t>(entry_base) + static_cast<size_t>(qi) * p.kv_heads + kvh) * p.hratio + gg;
+            *reinterpret_cast<float4*>(p.part_o + slot * D + v4 * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            if (v4 == 0) p.part_lse[slot] = g * p.scale + logf(L);
+        }
     }
+    // When this kernel runs beside the dense kernel (launched as its programmatic dependent),
+    // nothing else makes its completion imply the dense kernel's, yet the merge that follows is
+    // ordered after this kernel only.  One CTA therefore ends by waiting for the grids this launch
+    // depends on; the kernel cannot complete before that CTA does.  (Without the launch attribute
+    // the instruction returns at once.)
+    if (blockIdx.x == gridDim.x - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------

@@ -35,10 +35,49 @@ def shard_views(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, w
     return q[:, :, lo * group: hi * group], k_cache[:, :, lo:hi], v_cache[:, :, lo:hi]
 
 
+class HeadGather:
+    """The one optional collective of a sharded step: every rank gets all heads.
+
+    Buffers are allocated once: an NCCL all-gather writes the ranks' ``[B, 1, H/n, D]`` outputs
+    rank by rank into a staging buffer and one small kernel of this library puts the heads in
+    order in ``[B, 1, H, D]``.  Nothing synchronises, so a step and its gather can be captured in
+    one CUDA graph.  The result tensor is reused by every call."""
+
+    def __init__(self, out_shard: torch.Tensor, world: int, group=None):
+        b, one, h, d = out_shard.shape
+        if one != 1 or out_shard.element_size() != 2:
+            raise ValueError("expected a 16-bit [batch, 1, heads, head_dim] shard")
+        self.world, self.group = world, group
+        self.staged = torch.empty((world, b, h, d), dtype=out_shard.dtype, device=out_shard.device)
+        self.full = torch.empty((b, 1, world * h, d), dtype=out_shard.dtype, device=out_shard.device)
+
+    def __call__(self, out_shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return out_shard
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _native as N
+        shard = out_shard if out_shard.is_contiguous() else out_shard.contiguous()
+        b, _, h, d = shard.shape
+        dist.all_gather_into_tensor(self.staged.view(self.world * b, h, d), shard.view(b, h, d), group=self.group)
+        if shard.is_cuda:
+            stream = torch.cuda.current_stream(shard.device).cuda_stream
+            rc = N.load().pat_b200_reorder_heads(self.staged.data_ptr(), self.full.data_ptr(), self.world, b, h, d,
+                                                 C.c_void_p(stream))
+            if rc != 0:
+                raise RuntimeError(f"head reorder failed: {N.strerror(rc)}")
+        else:       # host tensors (multi-process tests of the partitioning on the CPU)
+            self.full.copy_(self.staged.permute(1, 0, 2, 3).reshape(b, 1, self.world * h, d))
+        return self.full
+
+
 def all_gather_heads(out_shard: torch.Tensor, world: int, group=None) -> torch.Tensor:
-    """Concatenate the ranks' ``[B, 1, H/n, D]`` outputs along the head axis (rank order)."""
+    """Concatenate the ranks' ``[B, 1, H/n, D]`` outputs along the head axis (rank order); one-off
+    form that allocates its buffers (``HeadGather`` keeps them)."""
     if world == 1:
         return out_shard
+    if out_shard.element_size() == 2:
+        return HeadGather(out_shard, world, group)(out_shard)
     import torch.distributed as dist
     shard = out_shard.contiguous()
     buf = torch.empty((world,) + tuple(shard.shape), dtype=shard.dtype, device=shard.device)

@@ -262,3 +262,62 @@ def make_values(w: Workload, device="cpu", kv_heads: slice | None = None):
     if str(device) != "cpu":
         q, k, v = q.to(device), k.to(device), v.to(device)
     return q, k, v
+
+
+# ---------------------------------------------------------------------------------------------
+# Counter-based cache values for the benchmark
+# ---------------------------------------------------------------------------------------------
+_MASK32 = 0xFFFFFFFF
+
+
+def _lsr(x, n: int):
+    """Logical right shift of an int64 tensor (torch's ``>>`` is arithmetic)."""
+    return (x >> n) & ((1 << (64 - n)) - 1)
+
+
+def _as_i64(c: int) -> int:
+    c &= (1 << 64) - 1
+    return c - (1 << 64) if c >= (1 << 63) else c
+
+
+def synthetic_pages(w: Workload, which: int, page_ids, device="cpu", kv_heads: slice | None = None):
+    """K (``which`` = 0) or V (1) values of the listed physical pages of workload ``w``:
+    ``[len(page_ids), page_size, heads, head_dim]`` in the workload's dtype, ~ N(0, 1) * 0.5.
+
+    Every element is a pure function of (workload seed, K or V, page, row, global KV head, d): a
+    64-bit mix of its linear index feeds a Box-Muller transform.  Any process can therefore
+    produce any subset of the cache - a GPU rank its head shard, chunk by chunk, on the device; the
+    CPU baseline only the pages of the requests it samples - without materialising the rest.
+    (The last bit of the transcendental functions may differ between devices; checks that need
+    identical bits read the values back from where they were generated.)
+    """
+    import torch
+    ids = torch.as_tensor(page_ids, dtype=torch.int64, device=device).reshape(-1)
+    hk = w.num_kv_heads
+    heads = range(hk)[kv_heads] if kv_heads is not None else range(hk)
+    h = torch.arange(heads.start, heads.stop, dtype=torch.int64, device=device)
+    r = torch.arange(w.page_size, dtype=torch.int64, device=device)
+    d = torch.arange(w.head_dim, dtype=torch.int64, device=device)
+    idx = ((ids[:, None, None, None] * w.page_size + r[None, :, None, None]) * hk + h[None, None, :, None]) \
+        * w.head_dim + d[None, None, None, :]
+    x = idx + _as_i64((w.seed * 2 + which + 1) * 0x9E3779B97F4A7C15)
+    x = (x ^ _lsr(x, 30)) * _as_i64(0xBF58476D1CE4E5B9)
+    x = (x ^ _lsr(x, 27)) * _as_i64(0x94D049BB133111EB)
+    x = x ^ _lsr(x, 31)
+    u1 = (((x >> 8) & 0xFFFFFF) + 1).to(torch.float32) * (1.0 / (1 << 24))          # (0, 1]
+    u2 = ((x >> 36) & 0xFFFFFF).to(torch.float32) * (2.0 * math.pi / (1 << 24))
+    z = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(u2)
+    return (z * 0.5).to(torch_dtype(w.dtype))
+
+
+def synthetic_queries(w: Workload, device="cpu", kv_heads: slice | None = None):
+    """``q [batch, 1, heads, head_dim]`` of the benchmark, drawn on the CPU generator with the
+    workload's seed (same bits in every process), optionally cut to a KV-head shard."""
+    import torch
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(w.seed)
+    q = (torch.randn(w.batch, 1, w.num_q_heads, w.head_dim, generator=gen) * 0.5).to(torch_dtype(w.dtype))
+    if kv_heads is not None:
+        heads = range(w.num_kv_heads)[kv_heads]
+        q = q[:, :, heads.start * w.group: heads.stop * w.group].contiguous()
+    return q if str(device) == "cpu" else q.to(device)

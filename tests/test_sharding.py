@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 
 from oracle import attention_oracle as O
 from pat_b200 import PrefixTreeCPP
-from pat_b200.sharding import all_gather_heads, kv_head_range, shard_views
+from pat_b200.sharding import HeadGather, all_gather_heads, kv_head_range, shard_views
 from pat_b200.workloads import make_values, scaled_down
 
 
@@ -43,6 +43,11 @@ def _worker(rank, world, port, ret):
         full = all_gather_heads(out_shard.contiguous(), world)
         ref, _ = O.paged_decode_attention(q, k, v, w.seq_lens, w.block_tables, scale)
         ok = torch.allclose(full, ref, atol=1e-6)
+        # the 16-bit form with buffers allocated once (on the GPU the reorder is a kernel of the library)
+        hg = HeadGather(out_shard.to(torch.bfloat16), world)
+        for _ in range(2):
+            full16 = hg(out_shard.to(torch.bfloat16))
+            ok = ok and torch.equal(full16, ref.to(torch.bfloat16)) and full16.data_ptr() == hg.full.data_ptr()
         # timing reduction used by the benchmark: max over ranks
         t = torch.tensor([float(rank + 1)])
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
