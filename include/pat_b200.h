@@ -126,6 +126,10 @@ typedef struct pat_work_options {
     int32_t dense_tile_ns;       /* estimated time of one 128-token dense tile; sizes the dense kernel's share
                                     of the SMs when it runs beside the streaming kernel.  0 = default,
                                     < 0 = the dense kernel gets every SM */
+    int32_t grow_slack_pages;    /* lists built from a tree: free page slots kept behind the page list of
+                                    every request's own last segment, so that pat_work_advance can append
+                                    pages in place.  0 = default (8), < 0 = none */
+    int32_t reserved;
 } pat_work_options;
 
 typedef struct pat_work_header {
@@ -148,9 +152,24 @@ typedef struct pat_work_header {
 pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int batch, int hratio,
                           int kv_heads, int page_size, int64_t num_cache_pages,
                           const pat_work_options* options, int* status);
-/* Same, straight from a packed tree. */
+/* Straight from a built tree (pat_tree_build; packing is not needed): every edge of the radix
+ * tree is one segment - its pages, attended by the requests that pass through it. */
 pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_t num_cache_pages,
                              const pat_work_options* options, int* status);
+/* One decode step later: the same requests, each with seq_lens[i] >= before and its table row
+ * extended by the pages the new tokens need (the reference rebuilds tree, plan and tables from
+ * scratch every step: prefix_attn/async_tree.py:23-30, and leaves them stale on multi-step
+ * decode: plugin/vllm/attention/backends/prefix_attn.py:430-438).  When every request that grew
+ * ends in a tree leaf of its own and the new pages fit the slack of the work list, tree and work
+ * list (blob and header: fetch them again) are updated in place and the call returns 1; the
+ * tree then equals the tree a fresh pat_tree_build of the new tables produces (its packed plan is
+ * dropped: pack again to get it).  Returns 0, with nothing changed, when the batch has to be
+ * rebuilt (other requests, a changed row, a shared last segment, slack used up); < 0 on a bad
+ * argument.  pat_tree_advance does the same for a tree alone. */
+int pat_work_advance(pat_work* w, pat_tree* t, const int32_t* seq_lens, const int32_t* block_table,
+                     int num_seqs, int row_stride);
+int pat_tree_advance(pat_tree* t, const int32_t* seq_lens, const int32_t* block_table, int num_seqs,
+                     int row_stride);
 void pat_work_destroy(pat_work* w);
 int pat_work_get_header(const pat_work* w, pat_work_header* out);
 /* int32 blob to copy to the device as is; *words receives its length */
@@ -186,7 +205,11 @@ typedef struct pat_decode_args {
     /* work list */
     const int32_t* work_blob;   /* device copy of pat_work_blob */
     pat_work_header work;       /* host copy of the header */
-    /* scratch for the per-(item, query, KV head) partial results; 32-byte aligned */
+    /* Scratch of pat_b200_workspace_bytes(...) bytes, 32-byte aligned: 256 bytes of control words,
+     * then the per-(item, query, KV head) partial results.  The control words must be zero when a
+     * workspace is used for the first time; every call that completes leaves them zero again (clear
+     * them after a call that reported a failed wait).  Calls that may overlap on the GPU need
+     * workspaces of their own. */
     void* workspace;
     size_t workspace_bytes;
     /* Optional device int32[4].  It must hold zeros when the call starts (the library does not

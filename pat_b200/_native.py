@@ -32,7 +32,8 @@ class PlanBucket(C.Structure):
 class WorkOptions(C.Structure):
     _fields_ = [("num_sms", C.c_int32), ("dense_min_rows", C.c_int32), ("chunk_tokens_min", C.c_int32),
                 ("chunk_tokens_max", C.c_int32), ("dense_piece_tokens_min", C.c_int32),
-                ("items_per_sm", C.c_int32), ("disable_dense", C.c_int32), ("dense_tile_ns", C.c_int32)]
+                ("items_per_sm", C.c_int32), ("disable_dense", C.c_int32), ("dense_tile_ns", C.c_int32),
+                ("grow_slack_pages", C.c_int32), ("reserved", C.c_int32)]
 
 
 class WorkHeader(C.Structure):
@@ -95,6 +96,8 @@ SIGNATURES = {
                                      C.c_int64, C.POINTER(WorkOptions), C.POINTER(C.c_int)]),
     "pat_work_from_tree": (C.c_void_p, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.POINTER(WorkOptions),
                                         C.POINTER(C.c_int)]),
+    "pat_work_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "pat_tree_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "pat_work_destroy": (None, [C.c_void_p]),
     "pat_work_get_header": (C.c_int, [C.c_void_p, C.POINTER(WorkHeader)]),
     "pat_work_blob": (i32p, [C.c_void_p, C.POINTER(C.c_size_t)]),

@@ -27,7 +27,7 @@ class WorkConfig:
     """Tuning knobs of the work-list builder (0 = library default)."""
 
     __slots__ = ("num_sms", "dense_min_rows", "chunk_tokens_min", "chunk_tokens_max",
-                 "dense_piece_tokens_min", "items_per_sm", "disable_dense", "dense_tile_ns")
+                 "dense_piece_tokens_min", "items_per_sm", "disable_dense", "dense_tile_ns", "grow_slack_pages")
 
     def __init__(self, **kw):
         for name in self.__slots__:
@@ -70,6 +70,9 @@ def set_default_config(cfg: Optional[WorkConfig]) -> None:
     _default_config = cfg
 
 
+_WS_HEAD = 256      # bytes of control words at the head of a workspace (include/pat_b200.h)
+
+
 def _sm_count(device: torch.device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
@@ -78,7 +81,7 @@ def _sm_count(device: torch.device) -> int:
 class DeviceWork:
     """A work list on one device: the int32 blob plus the host header."""
 
-    def __init__(self, handle: int, device: torch.device):
+    def __init__(self, handle: int, device: torch.device, keep_native: bool = False):
         lib = N.load()
         self.header = N.WorkHeader()
         lib.pat_work_get_header(handle, C.byref(self.header))
@@ -91,6 +94,9 @@ class DeviceWork:
         self._host = host                       # kept alive: the copy below is asynchronous
         self.blob = host.to(device, non_blocking=True)
         self.device = device
+        self._handle = handle if keep_native else None     # native list, kept to be advanced in place
+        self._host_alt = None                   # second pinned buffer, used alternately by refresh()
+        self._host_busy = {}                    # id(host buffer) -> event of its last upload
         # The copy runs on the stream that is current in THIS thread (a plan-building worker thread
         # uses the default stream); the kernels may be launched on another one.  The event lets the
         # first launch on a different stream wait for the upload.
@@ -102,9 +108,55 @@ class DeviceWork:
             self._uploaded.record(st)
             self._upload_stream = st.cuda_stream
         self._ordered = set()                   # streams already ordered after the upload
-        self._scratch = {}                      # (stream, bytes) -> workspace tensor
+        self._scratch = {}                      # stream -> workspace tensor
         self._args = None                       # (key, DecodeArgs) of the last call
-        lib.pat_work_destroy(handle)
+        # One workspace is allocated with the work list (sized for head_dim 128, the larger of the
+        # two supported), so that the first call - which may sit inside a stream capture - does not
+        # have to allocate and clear one.
+        self._spare = None
+        if device.type == "cuda":
+            self._spare = self._new_workspace(lib.pat_b200_workspace_bytes(C.byref(self.header), 1, 128), device)
+        if not keep_native:
+            lib.pat_work_destroy(handle)
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h:
+            try:
+                N.load().pat_work_destroy(h)
+            except Exception:
+                pass
+            self._handle = None
+
+    def refresh(self) -> None:
+        """After the native list was advanced in place: copy it to the device again, into the SAME
+        device buffer and on the current stream, so that launches on that stream before and after
+        see the old and the new list respectively.  The blob's address and the item counts do not
+        change, so a CUDA graph captured around the op stays valid."""
+        lib = N.load()
+        lib.pat_work_get_header(self._handle, C.byref(self.header))
+        words = C.c_size_t()
+        ptr = lib.pat_work_blob(self._handle, C.byref(words))
+        # two pinned buffers take turns: the previous upload may still be reading the other one
+        if self._host_alt is None:
+            self._host_alt = torch.empty_like(self._host, pin_memory=self.device.type == "cuda")
+        self._host, self._host_alt = self._host_alt, self._host
+        busy = self._host_busy.get(id(self._host))
+        if busy is not None:
+            busy.synchronize()
+        C.memmove(self._host.data_ptr(), ptr, words.value * 4)
+        self.blob.copy_(self._host, non_blocking=True)
+        if self.device.type == "cuda":
+            st = torch.cuda.current_stream(self.device)
+            ev = self._host_busy.get(id(self._host))
+            if ev is None:
+                ev = torch.cuda.Event()
+                self._host_busy[id(self._host)] = ev
+            ev.record(st)
+            self._uploaded, self._upload_stream = ev, st.cuda_stream
+            self._ordered = set()
+        if self._args is not None:              # same pointers, new header
+            self._args[1].work = self.header
 
     def order_after_upload(self, stream) -> None:
         """Makes ``stream`` wait for the upload of the blob (once per stream)."""
@@ -112,19 +164,31 @@ class DeviceWork:
         if self._uploaded is None or h == self._upload_stream or h in self._ordered:
             return
         if torch.cuda.is_current_stream_capturing():
-            # an event recorded outside a capture cannot be waited for inside it: settle it on the host
-            self._uploaded.synchronize()
-        else:
-            stream.wait_event(self._uploaded)
+            # Nothing is launched during a capture, and neither a wait for an event recorded outside
+            # it nor a host-side synchronisation may be issued here.  Replays come after the capture
+            # has ended; whoever captures a step has run it (or synchronised) before, as a capture
+            # needs anyway.
+            return
+        stream.wait_event(self._uploaded)
         self._ordered.add(h)
+
+    @staticmethod
+    def _new_workspace(nbytes: int, device) -> torch.Tensor:
+        ws = torch.empty(max(int(nbytes), _WS_HEAD), dtype=torch.uint8, device=device)
+        ws[:_WS_HEAD].zero_()                   # the control words start at zero
+        return ws
 
     def workspace(self, nbytes: int, stream, device) -> torch.Tensor:
         """Scratch for the partial results, reused by every call with this work list on ``stream``
-        (calls on one stream run one after the other, so they can share it)."""
-        key = (stream.cuda_stream, nbytes)
+        (calls on one stream run one after the other, so they can share it; calls on different
+        streams get different ones)."""
+        key = stream.cuda_stream
         ws = self._scratch.get(key)
-        if ws is None:
-            ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        if ws is None or ws.numel() < nbytes:
+            if self._spare is not None and self._spare.numel() >= nbytes:
+                ws, self._spare = self._spare, None
+            else:
+                ws = self._new_workspace(nbytes, device)
             self._scratch[key] = ws
         return ws
 
@@ -164,7 +228,7 @@ class DeviceWork:
         handle = lib.pat_work_from_tree(tree_handle, hratio, kv_heads, 0, C.byref(opts), C.byref(status))
         if not handle:
             raise RuntimeError(f"invalid plan: {N.strerror(status.value)}")
-        return cls(handle, device)
+        return cls(handle, device, keep_native=True)
 
 
 # --------------------------------------------------------------------------- native scheduler
@@ -180,55 +244,81 @@ class KernelInfo:
     """Plan produced by ``PrefixTreeCPP.pack_schedule`` (reference
     ``csrc/prefix_tree.h:7-39``): per-bucket int32 CPU tensors until
     ``to_gpu(device)`` moves them - and builds and uploads the device work
-    list the kernels consume."""
+    list the kernels consume.
+
+    The plan lives in the native tree; the tensors are only made (and moved) when one of the
+    fields is read.  The kernels here never read them - they run from the work list - so a decode
+    loop that just builds, packs, calls ``to_gpu`` and passes the tree to the op pays for none
+    of the per-bucket tensors and their host-to-device copies."""
+
+    _FIELDS = ("q_tables", "block_tables", "num_seqs_per_CTAs", "CTA_ranks", "kv_in_CTAs", "MNWs",
+               "num_split_per_seq", "max_split_per_seq", "max_seqs_in_CTA", "max_blocks_in_CTA")
 
     def __init__(self, owner: "PrefixTreeCPP"):
         self._owner = owner
-        self.q_tables: List[torch.Tensor] = []
-        self.block_tables: List[torch.Tensor] = []
-        self.num_seqs_per_CTAs: List[torch.Tensor] = []
-        self.CTA_ranks: List[torch.Tensor] = []
-        self.kv_in_CTAs: List[torch.Tensor] = []
-        self.MNWs: List[List[int]] = []
-        self.num_split_per_seq: torch.Tensor = torch.zeros(0, dtype=torch.int32)
-        self.max_split_per_seq = 0
-        self.max_seqs_in_CTA = 0
-        self.max_blocks_in_CTA = 0
+        self._vals = None           # field values, once read
+        self._device = None         # where to_gpu sent the plan
         self._work = {}
 
-    def _refresh(self):
+    def _invalidate(self):
+        """The native plan changed (a pack, or an in-place advance of the tree)."""
+        self._vals = None
+        self._work = {}
+
+    def __getattr__(self, name):
+        if name in KernelInfo._FIELDS:
+            if self._vals is None:
+                self._vals = self._read()
+            return self._vals[name]
+        raise AttributeError(name)
+
+    def __setattr__(self, name, value):
+        if name in KernelInfo._FIELDS:
+            if self._vals is None:
+                self._vals = self._read()
+            self._vals[name] = value
+        else:
+            object.__setattr__(self, name, value)
+
+    def _read(self):
         lib = N.load()
-        h = self._owner._handle
-        self.q_tables, self.block_tables, self.num_seqs_per_CTAs = [], [], []
-        self.CTA_ranks, self.kv_in_CTAs, self.MNWs = [], [], []
+        o = self._owner
+        o._ensure_packed()
+        h = o._handle
+        v = dict(q_tables=[], block_tables=[], num_seqs_per_CTAs=[], CTA_ranks=[], kv_in_CTAs=[], MNWs=[])
         view = N.BucketView()
         for i in range(lib.pat_tree_num_buckets(h)):
             lib.pat_tree_bucket(h, i, C.byref(view))
-            self.MNWs.append([view.mnw[0], view.mnw[1], view.mnw[2]])
-            self.q_tables.append(_view_i32(view.q_table, (view.ctas, view.max_seqs)))
-            self.block_tables.append(_view_i32(view.block_table, (view.ctas, view.max_blocks)))
-            self.num_seqs_per_CTAs.append(_view_i32(view.num_seqs, (view.ctas,)))
-            self.CTA_ranks.append(_view_i32(view.cta_ranks, (view.ctas,)))
-            self.kv_in_CTAs.append(_view_i32(view.kv_in_cta, (view.ctas,)))
+            v["MNWs"].append([view.mnw[0], view.mnw[1], view.mnw[2]])
+            v["q_tables"].append(_view_i32(view.q_table, (view.ctas, view.max_seqs)))
+            v["block_tables"].append(_view_i32(view.block_table, (view.ctas, view.max_blocks)))
+            v["num_seqs_per_CTAs"].append(_view_i32(view.num_seqs, (view.ctas,)))
+            v["CTA_ranks"].append(_view_i32(view.cta_ranks, (view.ctas,)))
+            v["kv_in_CTAs"].append(_view_i32(view.kv_in_cta, (view.ctas,)))
         n = C.c_int(0)
         ptr = lib.pat_tree_split_per_seq(h, C.byref(n))
-        self.num_split_per_seq = _view_i32(ptr, (n.value,))
+        v["num_split_per_seq"] = _view_i32(ptr, (n.value,)) if o._packed_once else torch.zeros(0, dtype=torch.int32)
         mx = (C.c_int32 * 3)()
         lib.pat_tree_maxima(h, mx)
-        self.max_split_per_seq, self.max_seqs_in_CTA, self.max_blocks_in_CTA = mx[0], mx[1], mx[2]
-        self._work = {}
+        v["max_split_per_seq"], v["max_seqs_in_CTA"], v["max_blocks_in_CTA"] = mx[0], mx[1], mx[2]
+        if self._device is not None:
+            self._move(v, self._device)
+        return v
+
+    @staticmethod
+    def _move(v, device):
+        move = lambda t: t.to(device, non_blocking=True)
+        for name in ("q_tables", "block_tables", "num_seqs_per_CTAs", "CTA_ranks", "kv_in_CTAs"):
+            v[name] = [move(t) for t in v[name]]
+        v["num_split_per_seq"] = move(v["num_split_per_seq"])
 
     def to_gpu(self, device: Union[torch.device, str]) -> None:
         device = torch.device(device)
         if device.type == "cuda" and device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
-        move = lambda t: t.to(device, non_blocking=True)
-        self.q_tables = [move(t) for t in self.q_tables]
-        self.block_tables = [move(t) for t in self.block_tables]
-        self.num_seqs_per_CTAs = [move(t) for t in self.num_seqs_per_CTAs]
-        self.CTA_ranks = [move(t) for t in self.CTA_ranks]
-        self.kv_in_CTAs = [move(t) for t in self.kv_in_CTAs]
-        self.num_split_per_seq = move(self.num_split_per_seq)
+        self._device = device
+        if self._vals is not None:
+            self._move(self._vals, device)
         if device.type == "cuda":
             self.device_work(device)
             check_status(device, synchronize=False)     # a failed wait of an earlier step surfaces here
@@ -264,6 +354,9 @@ class PrefixTreeCPP:
         self._kernel_info = KernelInfo(self)
         self._hratio = 1
         self._kv_heads = 8
+        self._pack_args = None          # arguments of the last pack_schedule
+        self._packed = False            # the native tree holds a plan for its current state
+        self._packed_once = False
 
     def __del__(self):
         h = getattr(self, "_handle", None)
@@ -322,6 +415,7 @@ class PrefixTreeCPP:
         else:
             arr, ptr, n = None, None, 0
         rc = lib.pat_tree_pack(self._handle, ptr, n, int(HRatio), int(kvHead), int(bool(use_compute_model)))
+        self._pack_args = (arr, int(HRatio), int(kvHead), int(bool(use_compute_model)))
         if rc == -2:
             raise IndexError(N.strerror(rc))
         if rc == -3:
@@ -331,7 +425,74 @@ class PrefixTreeCPP:
         if rc != 0:
             raise RuntimeError(f"pack_schedule failed: {N.strerror(rc)}")
         self._hratio, self._kv_heads = int(HRatio), int(kvHead)
-        self._kernel_info._refresh()
+        self._packed = self._packed_once = True
+        self._kernel_info._invalidate()
+
+    def _ensure_packed(self) -> None:
+        """Packs again after an in-place advance dropped the plan (same arguments as last time)."""
+        if self._packed or self._pack_args is None:
+            return
+        arr, hratio, kv_heads, ucm = self._pack_args
+        ptr, n = (arr.ctypes.data, arr.shape[0]) if arr is not None else (None, 0)
+        rc = N.load().pat_tree_pack(self._handle, ptr, n, hratio, kv_heads, ucm)
+        if rc != 0:
+            raise RuntimeError(f"pack_schedule failed: {N.strerror(rc)}")
+        self._packed = True
+
+    def advance(self, seq_lens, block_table: torch.Tensor, device=None) -> bool:
+        """One decode step later: the same requests, each at least as long as before, each table row
+        extended by the pages its new tokens need.  Returns ``True`` when tree and device work list
+        were updated in place - the tree is then the tree a fresh ``build_radix_tree`` of the new
+        tables would give, ``kernel_info`` is re-packed when (and only if) it is read, and the work
+        list is re-uploaded into the same device buffer on the current stream.  Returns ``False``,
+        with nothing changed, when the batch has to be rebuilt: other requests, a row whose old part
+        changed, a request that shares its last segment, or no room left for new pages.
+
+        The reference builds tree, plan and tables from scratch in every step
+        (``prefix_attn/async_tree.py:23-30``) and leaves them stale during multi-step decode
+        (``plugin/vllm/attention/backends/prefix_attn.py:430-438``)."""
+        lib = N.load()
+        if isinstance(seq_lens, torch.Tensor):
+            lens = np.ascontiguousarray(seq_lens.numpy(), dtype=np.int32)
+        else:
+            lens = np.asarray(seq_lens, dtype=np.int32)
+        if not isinstance(block_table, torch.Tensor) or block_table.dtype != torch.int32 or \
+                block_table.device.type != "cpu" or block_table.dim() != 2:
+            raise RuntimeError("block_table must be a 2-D CPU Int32 Tensor")
+        table = np.ascontiguousarray(block_table.numpy())
+        if lens.shape[0] != table.shape[0]:
+            return False
+        info = self._kernel_info
+        works = list(info._work.values())
+        if len(works) > 1:
+            return False                        # several devices / option sets: rebuild
+        if works:
+            if works[0]._handle is None:
+                return False
+            rc = lib.pat_work_advance(works[0]._handle, self._handle, lens.ctypes.data, table.ctypes.data,
+                                      table.shape[0], table.shape[1])
+        else:
+            rc = lib.pat_tree_advance(self._handle, lens.ctypes.data, table.ctypes.data,
+                                      table.shape[0], table.shape[1])
+        if rc < 0:
+            raise RuntimeError(f"advance failed: {N.strerror(rc)}")
+        if rc == 0:
+            return False
+        self._packed = False
+        info._vals = None                       # the plan is stale; the work list was advanced with the tree
+        if works:
+            works[0].refresh()
+        return True
+
+    def _max_split(self) -> int:
+        mx = (C.c_int32 * 3)()
+        N.load().pat_tree_maxima(self._handle, mx)
+        return mx[0]
+
+    def _batch(self) -> int:
+        n = C.c_int(0)
+        N.load().pat_tree_split_per_seq(self._handle, C.byref(n))
+        return n.value
 
     # ---- inspection helpers (not in the reference binding) -----------------
     def nodes(self):
@@ -428,11 +589,8 @@ def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None,
            lse_out.data_ptr() if lse_out is not None else 0, status.data_ptr(), stream.cuda_stream,
            q.shape, q.stride(), k_cache.shape, k_cache.stride(), v_cache.stride(), out.stride(),
            q.dtype, float(scale), int(flags), int(wait_limit_us))
-    # Inside a stream capture the scratch must come from the graph's own memory pool (it has to
-    # live as long as the graph, not as long as this work list), so nothing is cached there.
-    capturing = torch.cuda.is_current_stream_capturing()
     cached = work._args
-    if cached is not None and cached[0] == key and not capturing:
+    if cached is not None and cached[0] == key:
         a = cached[1]
     else:
         B, _, H, D = q.shape
@@ -452,13 +610,13 @@ def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None,
         a.work_blob = work.blob.data_ptr()
         a.work = work.header
         need = lib.pat_b200_workspace_bytes(C.byref(work.header), H, D)
-        ws = (torch.empty(need, dtype=torch.uint8, device=q.device) if capturing
-              else work.workspace(need, stream, q.device))
+        # (a graph captured around this call refers to the work list's blob and scratch: keep the
+        # tree alive as long as the graph, like the tensors)
+        ws = work.workspace(need, stream, q.device)
         a.workspace, a.workspace_bytes = ws.data_ptr(), need
         a.status_word = status.data_ptr()
         a.wait_limit_us = int(wait_limit_us)
-        if not capturing:
-            work._args = (key, a)
+        work._args = (key, a)
     rc = lib.pat_b200_decode(C.byref(a), C.c_void_p(stream.cuda_stream))
     if rc != 0:
         raise RuntimeError(f"prefix_attn_with_kvcache failed: {N.strerror(rc)} ({rc})")
@@ -540,16 +698,20 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
             tree = inner
         _check(isinstance(tree, PrefixTreeCPP), "tree must be a PrefixTreeCPP")
         info = tree.kernel_info
-        max_split = info.max_split_per_seq
-        nsplit = info.num_split_per_seq
+        # the plan's own numbers, read from the native tree without making the plan tensors; a
+        # tree advanced in place has no packed plan (and the reference's split limit is a limit
+        # of its kernels, not of the work list used here)
+        max_split = tree._max_split() if tree._packed else 1
+        _check(info._device is not None and info._device.type == "cuda", "num_split_per_seq must be on CUDA")
+        _check(tree._batch() == B, f"num_split_per_seq must have shape {(B,)}")
     else:
         max_split = int(bound["max_split_per_seq"])
         nsplit = bound["num_split_per_seq"]
+        _check_index(nsplit, "num_split_per_seq", (B,))
     if max_split > 32:
         raise RuntimeError("Currently, only supports up to 32 splits per seq. Excessive splitting may reduce efficiency.")
     if max_split <= 0:
         raise RuntimeError("there is no case that a seq has no block")
-    _check_index(nsplit, "num_split_per_seq", (B,))
 
     if tree_form:
         _check(tree._hratio == ratio, "the plan was packed for a different HRatio than q / k_cache imply")

@@ -33,6 +33,8 @@ pat::WorkOptions to_options(const pat_work_options* o) {
     if (o->dense_piece_tokens_min > 0) w.dense_piece_tokens_min = o->dense_piece_tokens_min;
     if (o->items_per_sm > 0) w.items_per_sm = o->items_per_sm;
     if (o->dense_tile_ns != 0) w.dense_tile_ns = o->dense_tile_ns;
+    if (o->grow_slack_pages > 0) w.grow_slack_pages = o->grow_slack_pages;
+    if (o->grow_slack_pages < 0) w.grow_slack_pages = 0;
     if (o->disable_dense) { w.dense_rows = 0; w.dense_min_rows = 1 << 30; }
     return w;
 }
@@ -208,25 +210,44 @@ pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_
     int dummy;
     if (!status) status = &dummy;
     if (!t) { *status = PAT_ERR_BAD_ARGUMENT; return nullptr; }
+    pat_work* w = new (std::nothrow) pat_work();
+    if (!w) { *status = PAT_ERR_NO_MEMORY; return nullptr; }
     try {
-    const auto& bks = t->tree.buckets();
-    std::vector<pat_plan_bucket> views(bks.size());
-    for (size_t i = 0; i < bks.size(); ++i) {
-        views[i].ctas = bks[i].ctas;
-        views[i].q_stride = bks[i].max_seqs;
-        views[i].block_stride = bks[i].max_blocks;
-        views[i].reserved = 0;
-        views[i].q_table = bks[i].q_table.data();
-        views[i].block_table = bks[i].block_table.data();
-        views[i].num_seqs = bks[i].num_seqs.data();
-        views[i].kv_in_cta = bks[i].kv_lens.data();
-    }
-    return pat_work_create(views.data(), static_cast<int>(views.size()), t->tree.batch(), hratio, kv_heads,
-                           t->tree.block_size(), num_cache_pages, options, status);
+        const int rc = w->list.build_from_tree(t->tree, hratio, kv_heads, num_cache_pages, to_options(options));
+        *status = map_work_error(rc);
+        if (rc != 0) { delete w; return nullptr; }
+        return w;
     } catch (...) {
+        delete w;
         *status = PAT_ERR_NO_MEMORY;
         return nullptr;
     }
+}
+
+int pat_tree_advance(pat_tree* t, const int32_t* seq_lens, const int32_t* block_table, int num_seqs,
+                     int row_stride) {
+    if (!t) return PAT_ERR_BAD_ARGUMENT;
+    try {
+        std::vector<pat::Growth> growth;
+        const int rc = t->tree.plan_advance(seq_lens, block_table, num_seqs, row_stride, growth);
+        if (rc != 1) return rc < 0 ? PAT_ERR_BAD_ARGUMENT : 0;
+        t->tree.apply_advance(growth);
+        return 1;
+    } catch (...) { return PAT_ERR_NO_MEMORY; }
+}
+
+int pat_work_advance(pat_work* w, pat_tree* t, const int32_t* seq_lens, const int32_t* block_table,
+                     int num_seqs, int row_stride) {
+    if (!w || !t) return PAT_ERR_BAD_ARGUMENT;
+    try {
+        std::vector<pat::Growth> growth;
+        const int rc = t->tree.plan_advance(seq_lens, block_table, num_seqs, row_stride, growth);
+        if (rc != 1) return rc < 0 ? PAT_ERR_BAD_ARGUMENT : 0;
+        if (w->list.header().batch != t->tree.batch() || w->list.can_advance(growth) != 1) return 0;
+        w->list.advance(growth);        // the page pointers in `growth` point into the caller's table
+        t->tree.apply_advance(growth);
+        return 1;
+    } catch (...) { return PAT_ERR_NO_MEMORY; }
 }
 
 void pat_work_destroy(pat_work* w) { delete w; }

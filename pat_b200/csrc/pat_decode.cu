@@ -95,8 +95,10 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
                         a.v_head_stride, a.v_row_stride, a.v_page_stride);
     if (rc != PAT_OK) return rc;
 
+    // workspace: control words, then the partial outputs, then the partial LSEs
     const size_t rows = static_cast<size_t>(a.work.num_entries) * a.work.hratio;   // hratio rows per entry
-    float* part_o = static_cast<float*>(a.workspace);
+    int32_t* sync_words = static_cast<int32_t*>(a.workspace);
+    float* part_o = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + kWorkspaceHeadBytes);
     float* part_lse = part_o + rows * D;
 
     AttnParams p{};
@@ -126,8 +128,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     // streaming kernel as its programmatic dependent: it may start as soon as every dense CTA is
     // running (each signals that at its top; the streaming kernel never waits for the dense
     // kernel's results), fills the SMs the dense kernel leaves and takes the others over as the
-    // dense CTAs retire.  The merge kernel is an ordinary launch and waits for both.
+    // dense CTAs retire.  The merge kernel is an ordinary launch: stream order makes it wait for the
+    // streaming kernel, and for the dense kernel it waits on a word in the workspace that the last
+    // dense CTA sets (every dense CTA is running or done before the streaming kernel may start, so
+    // that wait cannot outlast the dense kernel).
     const bool overlap = streaming && dense && !(a.flags & PAT_NO_OVERLAP);
+    const bool merge = !(a.flags & PAT_SKIP_MERGE);
+    int32_t* sync = (overlap && merge) ? sync_words : nullptr;
     if (dense) {
         // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
         static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
@@ -144,6 +151,7 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         DenseTcParams dp{};
         dp.a = pd;
         dp.cta_begin = a.work_blob + a.work.dense_cta_off;
+        dp.sync = sync;
         kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, stream>>>(dp, kmap, vmap);
         ++launches;
     }
@@ -173,8 +181,11 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         if (cudaLaunchKernelEx(&cfg, kern, p, kmap, vmap) != cudaSuccess) return PAT_ERR_CUDA;
         ++launches;
     }
-    if (!(a.flags & PAT_SKIP_MERGE)) {
+    if (merge) {
         MergeParams mp{};
+        mp.sync = sync;
+        mp.status = a.status_word;
+        mp.wait_ns = p.wait_ns;
         mp.part_o = part_o;
         mp.part_lse = part_lse;
         mp.indptr = a.work_blob + a.work.merge_indptr_off;
@@ -207,7 +218,7 @@ size_t pat_b200_workspace_bytes(const pat_work_header* work, int num_q_heads, in
     // one entry = hratio rows (the query heads of one KV head): partial outputs + partial LSEs
     const size_t rows = static_cast<size_t>(work->num_entries) * static_cast<size_t>(work->hratio);
     const size_t bytes = rows * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
-    return (bytes + 255) / 256 * 256 + 256;
+    return pat::kWorkspaceHeadBytes + (bytes + 255) / 256 * 256;
 }
 
 int pat_b200_last_launch_count(void) { return g_last_launches; }
@@ -238,8 +249,7 @@ int pat_b200_decode(const pat_decode_args* args, void* stream_handle) {
     if (!aligned16(a.work_blob)) return PAT_ERR_BAD_ARGUMENT;
     const size_t need = pat_b200_workspace_bytes(&a.work, a.num_q_heads, a.head_dim);
     // the dense kernel writes its partial rows with 32-byte stores
-    if (a.work.num_entries > 0 && (!a.workspace || a.workspace_bytes < need ||
-                                   (reinterpret_cast<uintptr_t>(a.workspace) & 31) != 0))
+    if (!a.workspace || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 31) != 0)
         return PAT_ERR_WORKSPACE;
 
     int dev = 0;

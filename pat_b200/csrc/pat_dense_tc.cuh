@@ -200,6 +200,11 @@ template <int N> __device__ __forceinline__ void tmem_st_f(uint32_t taddr, const
 struct DenseTcParams {
     AttnParams a;
     const int32_t* cta_begin;   // [num_ctas + 1] first dense item of each CTA
+    // Control words at the head of the workspace, or null.  Set when the streaming kernel runs
+    // beside this one: the merge kernel is then ordered after the streaming kernel only, so every
+    // CTA of this kernel counts itself out when its partial results are written and the last one
+    // sets the word the merge kernel waits for.
+    int32_t* sync;
 };
 
 // ------------------------------------------------------------------------------------
@@ -216,8 +221,22 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     const uint32_t base = smem_u32(tc_smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Called by thread 0 on every way out of the kernel, after a CTA-wide barrier that follows the
+    // CTA's last global store.
+    auto count_out = [&]() {
+        if (!dp.sync) return;
+        __threadfence();
+        const unsigned old = atomicInc(reinterpret_cast<unsigned*>(dp.sync + kSyncDenseCount), gridDim.x - 1);
+        if (old == gridDim.x - 1) {
+            __threadfence();
+            atomicExch(dp.sync + kSyncDenseDone, 1);
+        }
+    };
     if ((base & 1023u) != 0) {          // the swizzled layouts need a 1024-byte aligned window
-        if (tid == 0 && p.status) atomicExch(p.status, 10);
+        if (tid == 0) {
+            if (p.status) atomicExch(p.status, 10);
+            count_out();
+        }
         return;
     }
     const uint32_t sQ = base + L::kQOff, sK = base + L::kKOff, sV = base + L::kVOff;
@@ -234,10 +253,11 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     // If an earlier CTA of this call already gave up on a wait, do not start (uniform decision).
     if (tid == 0) *poisoned = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
     __syncthreads();
-    if (*poisoned) return;
-
     const int item_lo = __ldg(dp.cta_begin + blockIdx.x), item_hi = __ldg(dp.cta_begin + blockIdx.x + 1);
-    if (item_lo >= item_hi) return;     // a CTA without work (uniform)
+    if (*poisoned || item_lo >= item_hi) {      // an earlier failure, or a CTA without work (uniform)
+        if (tid == 0) count_out();
+        return;
+    }
 
     if (tid == 0) {
         tma_prefetch_desc(&kmap);
@@ -627,6 +647,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, kTcTmemCols);
+    if (tid == 0) count_out();
 }
 
 }  // namespace pat

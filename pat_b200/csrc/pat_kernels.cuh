@@ -238,12 +238,6 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
             if (v4 == 0) p.part_lse[slot] = g * p.scale + logf(L);
         }
     }
-    // When this kernel runs beside the dense kernel (launched as its programmatic dependent),
-    // nothing else makes its completion imply the dense kernel's, yet the merge that follows is
-    // ordered after this kernel only.  One CTA therefore ends by waiting for the grids this launch
-    // depends on; the kernel cannot complete before that CTA does.  (Without the launch attribute
-    // the instruction returns at once.)
-    if (blockIdx.x == gridDim.x - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------
@@ -258,32 +252,70 @@ struct MergeParams {
     float* lse_out;           // optional [batch, H]
     int64_t out_batch_stride, out_head_stride;
     int batch, num_q_heads, kv_heads, hratio;
+    // Control words at the head of the workspace, or null.  Set when the dense kernel ran beside
+    // the streaming kernel: this kernel is then ordered after the streaming kernel only, and waits
+    // here for the word the last dense CTA sets (see dense_tc_kernel).
+    int32_t* sync;
+    int32_t* status;          // optional
+    uint64_t wait_ns;
 };
+
+// Control words (int32) at the head of the workspace.
+constexpr int kSyncDenseCount = 0;   // dense CTAs that have finished; wraps to 0 with the last one
+constexpr int kSyncDenseDone = 1;    // 1 from the last dense CTA's exit until the last merge CTA's exit
+constexpr int kSyncMergeCount = 2;   // merge CTAs that have passed the wait; wraps to 0 with the last one
+constexpr int kWorkspaceHeadBytes = 256;
+
+__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
     constexpr int kPer = D / 32;   // floats per lane
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= p.batch * p.num_q_heads) return;
-    const int b = row / p.num_q_heads, h = row - b * p.num_q_heads;
-    const int kvh = h / p.hratio, g = h - kvh * p.hratio;
-    const int list = b * p.kv_heads + kvh;             // one list of entries per (request, KV head)
-    const int lo = __ldg(p.indptr + list), n = __ldg(p.indptr + list + 1) - lo;
-    const int32_t* ent = p.entries + lo;
-
+    const bool have_row = row < p.batch * p.num_q_heads;
+    // The merge lists come from the host (read-only for this kernel): they are fetched before the
+    // wait for the dense kernel.  The partial results are only read after it, with ordinary loads.
+    int b = 0, h = 0, g = 0, n = 0;
+    const int32_t* ent = p.entries;
+    size_t my_slot = 0;
+    if (have_row) {
+        b = row / p.num_q_heads;
+        h = row - b * p.num_q_heads;
+        const int kvh = h / p.hratio;
+        g = h - kvh * p.hratio;
+        const int list = b * p.kv_heads + kvh;             // one list of entries per (request, KV head)
+        const int lo = __ldg(p.indptr + list);
+        n = __ldg(p.indptr + list + 1) - lo;
+        ent = p.entries + lo;
+        if (lane < n) my_slot = static_cast<size_t>(__ldg(ent + lane)) * p.hratio + g;
+    }
+    if (p.sync) {
+        if (threadIdx.x == 0) {
+            // bounded: every dense CTA was running or done before the streaming kernel, which this
+            // launch is ordered after, could start
+            const uint64_t start = global_timer_ns();
+            bool ok = true;
+            for (uint32_t i = 1; ld_acquire_gpu(p.sync + kSyncDenseDone) == 0; ++i) {
+                if ((i & 63u) == 0 && global_timer_ns() - start > p.wait_ns) { ok = false; break; }
+            }
+            if (!ok && p.status) atomicExch(p.status, 20);
+        }
+        __syncthreads();
+    }
+    if (have_row) {
     // Lane i owns entry i (and i + 32, ...): its slot and LSE are loaded side by side, then the
     // partial rows are read four at a time (independent loads), the slot and weight of each
     // coming from the owning lane by shuffle.  A list rarely has more than 32 entries.
-    size_t my_slot = 0;
     float my_lse = -INFINITY;
-    if (lane < n) {
-        my_slot = static_cast<size_t>(__ldg(ent + lane)) * p.hratio + g;
-        my_lse = __ldg(p.part_lse + my_slot);
-    }
+    if (lane < n) my_lse = p.part_lse[my_slot];
     float gmax = my_lse;
     for (int i = lane + 32; i < n; i += 32)
-        gmax = fmaxf(gmax, __ldg(p.part_lse + static_cast<size_t>(__ldg(ent + i)) * p.hratio + g));
+        gmax = fmaxf(gmax, p.part_lse[static_cast<size_t>(__ldg(ent + i)) * p.hratio + g]);
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(kFullMask, gmax, d));
 
@@ -297,7 +329,7 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
             my_lse = -INFINITY;
             if (base + lane < n) {
                 my_slot = static_cast<size_t>(__ldg(ent + base + lane)) * p.hratio + g;
-                my_lse = __ldg(p.part_lse + my_slot);
+                my_lse = p.part_lse[my_slot];
             }
         }
         const float my_w = (my_lse == -INFINITY) ? 0.f : __expf(my_lse - gmax);    // 0 for lanes past the list
@@ -315,9 +347,9 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
                 w[k] = (i + k < cnt) ? __shfl_sync(kFullMask, my_w, src_lane) : 0.f;
                 const float* src = p.part_o + slot * D + lane * kPer;
                 if constexpr (kPer == 4) {
-                    x[k] = __ldg(reinterpret_cast<const float4*>(src));
+                    x[k] = *reinterpret_cast<const float4*>(src);
                 } else {
-                    const float2 y = __ldg(reinterpret_cast<const float2*>(src));
+                    const float2 y = *reinterpret_cast<const float2*>(src);
                     x[k] = make_float4(y.x, y.y, 0.f, 0.f);
                 }
             }
@@ -344,6 +376,15 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
         *reinterpret_cast<uint32_t*>(dst) = Elt<T>::pack(acc[0] * inv, acc[1] * inv);
     }
     if (p.lse_out && lane == 0) p.lse_out[row] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+    }
+    if (p.sync) {
+        // the last CTA past the wait clears the word for the next call
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned old = atomicInc(reinterpret_cast<unsigned*>(p.sync + kSyncMergeCount), gridDim.x - 1);
+            if (old == gridDim.x - 1) atomicExch(p.sync + kSyncDenseDone, 0);
+        }
+    }
 }
 
 }  // namespace pat

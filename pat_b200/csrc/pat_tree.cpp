@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstring>
 #include <map>
 
 namespace pat {
@@ -73,6 +74,7 @@ void Tree::insert(int seq, int seq_len, const int* pages, int left) {
             const int leaf = add_node(at, 1, seq_len, {seq}, pages, left);
             nodes_[at].children[head] = leaf;
             nodes_[at].child_keys.push_back(head);
+            leaf_[seq] = leaf;
             return;
         }
         const int child = it->second;
@@ -121,9 +123,13 @@ void Tree::insert(int seq, int seq_len, const int* pages, int left) {
             const int leaf = add_node(mid, 1, len, {seq}, rest, left - shared);
             nodes_[mid].children[rest[0]] = leaf;
             nodes_[mid].child_keys.push_back(rest[0]);
+            leaf_[seq] = leaf;
+        } else {
+            leaf_[seq] = mid;
         }
         return;
     }
+    leaf_[seq] = at;
 }
 
 int Tree::build_padded(const int32_t* seq_lens, const int32_t* table, int num_seqs, int row_stride) {
@@ -150,6 +156,12 @@ int Tree::build_padded(const int32_t* seq_lens, const int32_t* table, int num_se
                   table + static_cast<size_t>(i) * row_stride + counts[i], pool_.begin() + pos);
         pos += counts[i];
     }
+    leaf_.assign(num_seqs, 0);
+    seq_len_.assign(seq_lens, seq_lens + num_seqs);
+    row_start_ = starts;
+    row_pages_ = counts;
+    grown_.assign(num_seqs, {});
+    leaf_pages_.assign(num_seqs, {});
     for (int i = 0; i < num_seqs; ++i) insert(i, seq_lens[i], pool_.data() + starts[i], counts[i]);
     split_per_seq_.assign(num_seqs, 0);
     batch_ = num_seqs;
@@ -164,15 +176,77 @@ int Tree::build_ragged(const int32_t* seq_lens, const int32_t* flat, const int64
     if (total < 0 || (total > 0 && !flat)) return kTreeBadArgument;
     pool_.assign(flat, flat + total);
     nodes_.reserve(static_cast<size_t>(num_seqs) * 2 + 1);
+    leaf_.assign(num_seqs, 0);
+    seq_len_.assign(seq_lens, seq_lens + num_seqs);
+    row_start_.assign(num_seqs, 0);
+    row_pages_.assign(num_seqs, 0);
+    grown_.assign(num_seqs, {});
+    leaf_pages_.assign(num_seqs, {});
     for (int i = 0; i < num_seqs; ++i) {
         const int64_t lo = offsets[i], hi = offsets[i + 1];
         if (lo < 0 || hi < lo || hi > total) return kTreeBadArgument;
+        row_start_[i] = static_cast<size_t>(lo);
+        row_pages_[i] = static_cast<int>(hi - lo);
         insert(i, seq_lens[i], pool_.data() + lo, static_cast<int>(hi - lo));
     }
     split_per_seq_.assign(num_seqs, 0);
     batch_ = num_seqs;
     built_ = true;
     return kTreeOk;
+}
+
+int Tree::plan_advance(const int32_t* seq_lens, const int32_t* table, int num_seqs, int row_stride,
+                       std::vector<Growth>& out) const {
+    out.clear();
+    if (!built_ || num_seqs != batch_) return 0;
+    if (num_seqs > 0 && (!seq_lens || !table)) return kTreeBadArgument;
+    const int bs = block_size_;
+    for (int i = 0; i < num_seqs; ++i) {
+        const int old_len = seq_len_[i], new_len = seq_lens[i];
+        if (new_len < old_len) return 0;
+        const int old_np = old_len > 0 ? ceil_div(old_len, bs) : 0;
+        const int new_np = new_len > 0 ? ceil_div(new_len, bs) : 0;
+        if (new_np > row_stride) return kTreeBadArgument;
+        // the part of the row the tree was built from (and has grown by since) must be unchanged
+        const int32_t* row = table + static_cast<size_t>(i) * row_stride;
+        const int built_np = std::min(row_pages_[i], old_np);
+        if (built_np > 0 && std::memcmp(row, pool_.data() + row_start_[i], sizeof(int32_t) * built_np) != 0) return 0;
+        const std::vector<int32_t>& g = grown_[i];
+        if (built_np + static_cast<int>(g.size()) != old_np) return 0;
+        if (!g.empty() && std::memcmp(row + built_np, g.data(), sizeof(int32_t) * g.size()) != 0) return 0;
+        if (new_len == old_len) continue;
+        // a request that grows must end in a leaf of its own whose edge ends with the request
+        const TreeNode& leaf = nodes_[leaf_[i]];
+        if (old_len <= 0 || row_pages_[i] > old_np || leaf_[i] == 0 || !leaf.children.empty() || leaf.s_value != 1 ||
+            leaf.seq_indices.size() != 1 || leaf.seq_indices[0] != i)
+            return 0;
+        out.push_back(Growth{i, new_len - old_len, new_np - old_np, row + old_np});
+    }
+    return 1;
+}
+
+void Tree::apply_advance(const std::vector<Growth>& growth) {
+    for (const Growth& g : growth) {
+        TreeNode& leaf = nodes_[leaf_[g.seq]];
+        if (g.num_pages > 0) {
+            std::vector<int32_t>& buf = leaf_pages_[g.seq];
+            const int have = node_pages(leaf);
+            if (buf.empty()) {
+                buf.reserve(static_cast<size_t>(have) + 64);
+                buf.assign(leaf.pages, leaf.pages + have);
+            }
+            buf.insert(buf.end(), g.pages, g.pages + g.num_pages);
+            leaf.pages = buf.data();
+            leaf.num_pages = static_cast<int>(buf.size());
+            grown_[g.seq].insert(grown_[g.seq].end(), g.pages, g.pages + g.num_pages);
+        }
+        leaf.length += g.tokens;
+        seq_len_[g.seq] += g.tokens;
+    }
+    // a freshly built tree carries no plan
+    buckets_.clear();
+    std::fill(split_per_seq_.begin(), split_per_seq_.end(), 0);
+    max_split_ = max_seqs_ = max_blocks_ = 0;
 }
 
 int Tree::emit(const std::vector<int>& queries, int begin, int count, int mm,

@@ -62,6 +62,14 @@ struct Bucket {
     std::vector<int32_t> kv_lens;      // [ctas]
 };
 
+// Growth of one request between two decode steps (Tree::plan_advance).
+struct Growth {
+    int seq;
+    int tokens;                 // new valid tokens at the end of the request
+    int num_pages;              // pages appended to its table row
+    const int32_t* pages;       // points into the caller's table
+};
+
 enum TreeStatus : int {
     kTreeOk = 0,
     kTreeBadArgument = -1,
@@ -81,6 +89,21 @@ public:
     int build_ragged(const int32_t* seq_lens, const int32_t* flat, const int64_t* offsets, int num_seqs);
 
     int pack(const int32_t* mnws, int num_mnws, int hratio, int kv_heads, bool use_compute_model);
+
+    // --- in-place growth between decode steps ------------------------------------
+    // A decode step appends tokens (and now and then a page) to requests whose tables are
+    // otherwise unchanged.  When every request ends in a leaf that belongs to it alone, the tree
+    // a fresh build would produce from the new tables is this tree with longer leaf edges.
+    // plan_advance checks that (same batch, no request shrinks, the old part of every row
+    // unchanged, every growing request alone in its leaf) and lists the growth; it returns 1
+    // when the tree can grow in place, 0 when it has to be rebuilt, < 0 on a bad argument, and
+    // changes nothing.  apply_advance performs the growth and forgets the packed plan (a fresh
+    // tree has none).
+    int plan_advance(const int32_t* seq_lens, const int32_t* table, int num_seqs, int row_stride,
+                     std::vector<Growth>& out) const;
+    void apply_advance(const std::vector<Growth>& growth);
+    int leaf_of(int seq) const { return leaf_[seq]; }
+    int seq_len(int seq) const { return seq_len_[seq]; }
 
     // --- results -------------------------------------------------------------
     const std::vector<Bucket>& buckets() const { return buckets_; }
@@ -112,6 +135,12 @@ private:
     int batch_ = 0;
     bool built_ = false;
     std::vector<int32_t> pool_;   // private copy of every page list
+    std::vector<int> leaf_;       // node in which each request ends
+    std::vector<int32_t> seq_len_;
+    std::vector<size_t> row_start_;             // each request's row in pool_ (as built)
+    std::vector<int> row_pages_;                // pages of that row
+    std::vector<std::vector<int32_t>> grown_;   // pages appended to a request since the build
+    std::vector<std::vector<int32_t>> leaf_pages_;  // a grown leaf's page list (the node points here)
     std::vector<TreeNode> nodes_;
     std::vector<int32_t> split_per_seq_;
     std::vector<Bucket> buckets_;

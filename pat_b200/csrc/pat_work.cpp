@@ -24,13 +24,7 @@ struct FusedBox {            // boxes that share one page list
     std::vector<int32_t> queries;
 };
 
-struct Segment {             // pages attended by exactly the same fused boxes
-    std::vector<int32_t> queries;
-    std::vector<int32_t> pages;
-    int64_t tokens = 0;
-    int partial_tokens = 0;  // valid tokens of the (single, last) partial page, 0 if none
-    int32_t q_off = 0, page_off = 0;
-};
+using Segment = WorkSegment;  // pages attended by exactly the same fused boxes
 
 inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
@@ -40,6 +34,7 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                     int page_size, int64_t num_cache_pages, const WorkOptions& opt) {
     header_ = WorkHeader{};
     blob_.clear();
+    grow_.clear();
     if (num_buckets < 0 || batch <= 0 || hratio < 1 || hratio > 16 || kv_heads < 1 || page_size < 16 ||
         page_size % 16 != 0 || opt.stream_rows < hratio || (num_buckets > 0 && !buckets))
         return -1;
@@ -207,6 +202,43 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         }
     }
 
+    return finish(segs, batch, hratio, kv_heads, page_size, opt);
+}
+
+int WorkList::build_from_tree(const Tree& tree, int hratio, int kv_heads, int64_t num_cache_pages,
+                              const WorkOptions& opt) {
+    header_ = WorkHeader{};
+    blob_.clear();
+    grow_.clear();
+    const int batch = tree.batch(), page_size = tree.block_size();
+    if (batch <= 0 || hratio < 1 || hratio > 16 || kv_heads < 1 || page_size < 16 || page_size % 16 != 0 ||
+        opt.stream_rows < hratio)
+        return -1;
+    const std::vector<TreeNode>& nodes = tree.nodes();
+    std::vector<Segment> segs;
+    segs.reserve(nodes.size());
+    for (size_t n = 1; n < nodes.size(); ++n) {
+        const TreeNode& node = nodes[n];
+        if (node.length <= 0 || node.seq_indices.empty() || !node.pages) continue;
+        const int np = ceil_div(node.length, page_size);
+        Segment sg;
+        sg.queries.assign(node.seq_indices.begin(), node.seq_indices.end());
+        for (int32_t q : sg.queries)
+            if (q < 0 || q >= batch) return -3;
+        sg.pages.assign(node.pages, node.pages + np);
+        for (int32_t pg : sg.pages)
+            if (pg < 0 || (num_cache_pages > 0 && pg >= num_cache_pages)) return -4;
+        sg.tokens = node.length;
+        sg.partial_tokens = node.length % page_size;
+        const int only = sg.queries.size() == 1 ? sg.queries[0] : -1;
+        if (only >= 0 && node.children.empty() && tree.leaf_of(only) == static_cast<int>(n)) sg.owner = only;
+        segs.push_back(std::move(sg));
+    }
+    return finish(segs, batch, hratio, kv_heads, page_size, opt);
+}
+
+int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_heads, int page_size,
+                     const WorkOptions& opt) {
     // ---- 4. classes and chunk sizes ---------------------------------------------
     const int q_per_stream = std::max(1, opt.stream_rows / hratio);
     const int q_per_dense = opt.dense_rows > 0 ? std::max(1, opt.dense_rows / hratio) : 0;
@@ -236,6 +268,8 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         queries_sec.insert(queries_sec.end(), sg.queries.begin(), sg.queries.end());
         sg.page_off = static_cast<int32_t>(pages_sec.size());
         pages_sec.insert(pages_sec.end(), sg.pages.begin(), sg.pages.end());
+        // room to grow in place; a dense segment is never extended (its owner would need >= 17 rows)
+        if (sg.owner >= 0 && !is_dense(sg)) pages_sec.insert(pages_sec.end(), std::max(0, opt.grow_slack_pages), 0);
     }
 
     // ---- 5. streaming items -----------------------------------------------------
@@ -262,6 +296,9 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                 it.entry_base = num_entries;
                 it.kv_head = -1;
                 it.cost = kv;
+                // the item that holds the last tokens of a segment one request owns: remembered
+                // (through the sort below) as the item WorkList::advance extends
+                it.reserved = (sg.owner >= 0 && p1 == np) ? sg.owner + 1 : 0;
                 num_entries += it.nq * kv_heads;
                 for (int i = 0; i < it.nq; ++i)
                     for (int h = 0; h < kv_heads; ++h)
@@ -273,14 +310,34 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
     }
     std::stable_sort(stream_items.begin(), stream_items.end(),
                      [](const WorkItem& a, const WorkItem& b) { return a.cost > b.cost; });
+    bool any_owner = false;
+    for (const Segment& sg : segs) any_owner = any_owner || sg.owner >= 0;
+    if (any_owner) {
+        grow_.assign(static_cast<size_t>(batch), GrowSlot{});
+        for (size_t i = 0; i < stream_items.size(); ++i) {
+            WorkItem& it = stream_items[i];
+            if (it.reserved > 0) grow_[it.reserved - 1].item = static_cast<int32_t>(i);
+            it.reserved = 0;
+        }
+        for (const Segment& sg : segs) {
+            if (sg.owner < 0 || is_dense(sg)) continue;
+            GrowSlot& g = grow_[sg.owner];
+            g.next_page = sg.page_off + static_cast<int32_t>(sg.pages.size());     // made absolute once the blob is laid out
+            g.slack = std::max(0, opt.grow_slack_pages);
+            g.last_tokens = sg.partial_tokens > 0 ? sg.partial_tokens : page_size;
+        }
+    }
 
     // ---- 6. dense items: equal token shares per persistent CTA ------------------
     // The token ranges of the dense segments are laid end to end and cut into `shares` parts of
     // equal cost.  A share is executed by kv_heads x row_lanes CTAs at the same time
     // (CTA id = (share * kv_heads + head) * row_lanes + lane): one per KV head and per 128-row
-    // chunk of the queries (chunk c runs on lane c % row_lanes).  The CTAs of a share walk the
-    // same pages side by side, so a 2 KB cache row (all heads of a token) is fetched from HBM
-    // within a short window and the second row chunk finds it in L2.
+    // chunk of the queries.  Inside a share every 128-row chunk of every piece goes to the row
+    // lane that has the least work so far: the chunks of one piece land on different lanes and
+    // run side by side (a 2 KB cache row - all heads of a token - is then fetched from HBM within a
+    // short window and the second row chunk finds it in L2), and pieces with a single chunk (few
+    // rows, as in the lower levels of a deep tree) fill both lanes evenly instead of queueing on
+    // the first.
     struct DenseSeg { const Segment* sg; int chunks; };
     std::vector<DenseSeg> dsegs;
     int max_chunks = 1;
@@ -299,9 +356,12 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
         int64_t granule = 64;
         while (granule % page_size != 0) granule += 64;
         const int64_t min_piece = std::max<int64_t>(granule, opt.dense_piece_tokens_min);
-        auto passes = [&](const DenseSeg& d) { return static_cast<int64_t>(ceil_div(d.chunks, row_lanes)); };
+        // cost unit: tokens x row chunks (what the row lanes of a share work off together); every
+        // item costs about as much as kItemTokens more tokens (pipeline fill, epilogue)
+        constexpr int64_t kItemTokens = 256;
+        auto passes = [&](const DenseSeg& d) { return static_cast<int64_t>(d.chunks); };
         int64_t total_cost = 0;
-        for (const DenseSeg& d : dsegs) total_cost += d.sg->tokens * passes(d);
+        for (const DenseSeg& d : dsegs) total_cost += (d.sg->tokens + kItemTokens) * passes(d);
         const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / (static_cast<int64_t>(kv_heads) * row_lanes));
         int64_t share_limit = max_shares;
         if (opt.dense_tile_ns > 0 && header_.stream_tokens > 0) {
@@ -320,7 +380,9 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                 const int64_t group = static_cast<int64_t>(kv_heads) * row_lanes;      // CTAs per share
                 int64_t chunk_sum = 0;
                 for (const DenseSeg& d : dsegs) chunk_sum += d.chunks;
-                const double tile_ns = static_cast<double>(total_cost) * group / 128.0 * opt.dense_tile_ns;
+                int64_t token_chunks = 0;
+                for (const DenseSeg& d : dsegs) token_chunks += d.sg->tokens * d.chunks;
+                const double tile_ns = static_cast<double>(token_chunks) * kv_heads / 128.0 * opt.dense_tile_ns;
                 for (int64_t sh = 1; sh < max_shares; ++sh) {
                     const double items = static_cast<double>(chunk_sum * kv_heads + sh * group);
                     if (kFixedNs + (tile_ns + items * kItemNs) / static_cast<double>(sh * group) <= kWindowShare * window_ns) {
@@ -330,47 +392,62 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
                 }
             }
         }
-        const int64_t shares = std::min<int64_t>(share_limit, std::max<int64_t>(1, total_cost / min_piece));
+        const int64_t shares = std::min<int64_t>(share_limit, std::max<int64_t>(1, total_cost / row_lanes / min_piece));
         struct Piece { const DenseSeg* d; int64_t pos, take; };
-        std::vector<std::vector<Piece>> share_pieces(1);
-        int64_t used = 0, assigned = 0;
-        int64_t target = (total_cost + shares - 1) / shares;
-        auto can_advance = [&]() { return static_cast<int64_t>(share_pieces.size()) < shares; };
-        auto next_share = [&]() {
-            share_pieces.emplace_back();
-            used = 0;
-            // re-balance: what is left, spread over the shares that are left
-            const int64_t left = shares - static_cast<int64_t>(share_pieces.size()) + 1;
-            target = (total_cost - assigned + left - 1) / left;
-        };
-        for (size_t di = 0; di < dsegs.size(); ++di) {
-            const DenseSeg& d = dsegs[di];
-            const int64_t tokens = d.sg->tokens, w = passes(d);
-            int64_t pos = 0;
-            while (pos < tokens) {
-                int64_t cap = (target - used + w - 1) / w;                  // tokens of this segment that still fit
-                if (!can_advance()) cap = tokens - pos;                     // the last share takes what is left
-                else if (cap < min_piece / 2 && used > 0) { next_share(); continue; }
-                int64_t take = std::min(tokens - pos, std::max(cap, granule));
-                if (take < tokens - pos) take = std::max<int64_t>(granule, (take + granule - 1) / granule * granule);
-                take = std::min(take, tokens - pos);
-                // do not leave a sliver behind
-                if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
-                share_pieces.back().push_back(Piece{&d, pos, take});
-                used += take * w;
-                assigned += take * w;
-                pos += take;
-                if (used >= target && can_advance() && (pos < tokens || di + 1 < dsegs.size())) next_share();
+        // Walk the segments and fill one share after the other up to `target` cost units, cutting
+        // segments on granule boundaries where a share is full.  How many pieces that makes - and
+        // with it the per-item part of the cost - is only known afterwards, so the target starts
+        // at the even split and is raised a little until the shares at hand hold everything.
+        std::vector<std::vector<Piece>> share_pieces;
+        auto cut = [&](int64_t target) {
+            share_pieces.assign(1, {});
+            int64_t used = 0;
+            for (const DenseSeg& d : dsegs) {
+                const int64_t tokens = d.sg->tokens, w = passes(d);
+                int64_t pos = 0;
+                while (pos < tokens) {
+                    int64_t cap = (target - used) / w - kItemTokens;            // tokens of this segment that still fit
+                    cap = cap / granule * granule;
+                    if (cap < granule && used > 0) {                            // full: open the next share
+                        share_pieces.emplace_back();
+                        used = 0;
+                        continue;
+                    }
+                    int64_t take = std::min(tokens - pos, std::max(cap, granule));
+                    // do not leave a sliver behind
+                    if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
+                    share_pieces.back().push_back(Piece{&d, pos, take});
+                    used += (take + kItemTokens) * w;
+                    pos += take;
+                }
             }
-        }
+            return static_cast<int64_t>(share_pieces.size());
+        };
+        int64_t target = (total_cost + shares - 1) / shares;
+        while (cut(target) > shares) target += std::max<int64_t>(target / 32, 1);
+        struct LaneJob { const Piece* pc; int chunk; };
+        std::vector<std::vector<LaneJob>> lane_jobs(row_lanes);
         for (const auto& pieces : share_pieces) {
+            std::vector<int64_t> load(row_lanes, 0);
+            for (auto& jobs : lane_jobs) jobs.clear();
+            for (const Piece& pc : pieces) {
+                for (int chunk = 0; chunk < pc.d->chunks; ++chunk) {
+                    int lane = 0;
+                    for (int l = 1; l < row_lanes; ++l)
+                        if (load[l] < load[lane]) lane = l;
+                    lane_jobs[lane].push_back(LaneJob{&pc, chunk});
+                    load[lane] += pc.take + kItemTokens;
+                }
+            }
             for (int h = 0; h < kv_heads; ++h) {
                 for (int lane = 0; lane < row_lanes; ++lane) {
                     cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
-                    for (const Piece& pc : pieces) {
+                    for (const LaneJob& job : lane_jobs[lane]) {
+                        const Piece& pc = *job.pc;
                         const Segment* sg = pc.d->sg;
                         const int nq_all = static_cast<int>(sg->queries.size());
-                        for (int chunk = lane; chunk < pc.d->chunks; chunk += row_lanes) {
+                        {
+                            const int chunk = job.chunk;
                             const int q0 = chunk * q_per_dense;
                             WorkItem it{};
                             it.q_off = sg->q_off + q0;
@@ -454,7 +531,43 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
     header_.max_page_id = -1;
     for (int32_t pg : pages_sec) header_.max_page_id = std::max(header_.max_page_id, pg);
     header_.unique_tokens = unique_tokens;
+    for (GrowSlot& g : grow_)
+        if (g.item >= 0) g.next_page += static_cast<int32_t>(pages_off);
     return 0;
+}
+
+int WorkList::can_advance(const std::vector<Growth>& growth) const {
+    if (grow_.empty()) return growth.empty() ? 1 : 0;
+    for (const Growth& gr : growth) {
+        if (gr.seq < 0 || gr.seq >= static_cast<int>(grow_.size())) return 0;
+        const GrowSlot& g = grow_[gr.seq];
+        if (g.item < 0 || gr.num_pages > g.slack) return 0;
+        // the new tokens must fill the last page first and then exactly the appended pages
+        const int room = header_.page_size - g.last_tokens;
+        const int beyond = gr.tokens - room;
+        const int need = beyond > 0 ? ceil_div(beyond, header_.page_size) : 0;
+        if (need != gr.num_pages) return 0;
+    }
+    return 1;
+}
+
+void WorkList::advance(const std::vector<Growth>& growth) {
+    for (const Growth& gr : growth) {
+        GrowSlot& g = grow_[gr.seq];
+        int32_t* item = blob_.data() + header_.items_off + static_cast<size_t>(g.item) * 8;
+        item[3] += gr.tokens;                   // kv_len
+        item[6] += gr.tokens;                   // cost
+        for (int i = 0; i < gr.num_pages; ++i) {
+            blob_[static_cast<size_t>(g.next_page) + i] = gr.pages[i];
+            header_.max_page_id = std::max(header_.max_page_id, gr.pages[i]);
+        }
+        g.next_page += gr.num_pages;
+        g.slack -= gr.num_pages;
+        g.last_tokens = (g.last_tokens + gr.tokens - 1) % header_.page_size + 1;
+        header_.unique_tokens += gr.tokens;
+        header_.stream_tokens += gr.tokens;
+        header_.stream_unique_tokens += gr.tokens;
+    }
 }
 
 }  // namespace pat

@@ -28,6 +28,8 @@
 #include <cstdint>
 #include <vector>
 
+#include "pat_tree.h"
+
 namespace pat {
 
 struct PlanBucketView {
@@ -54,6 +56,9 @@ struct WorkOptions {
     // it needs to finish within the time the streaming kernel needs for its HBM traffic.
     // < 0: the dense kernel is cut for every SM.
     int dense_tile_ns = 1600;
+    // Pages of slack behind the page list of a segment that one request owns alone (only in
+    // lists built straight from a tree): room for WorkList::advance to append pages in place.
+    int grow_slack_pages = 8;
 };
 
 // One work item = 8 int32 on the device.
@@ -96,17 +101,48 @@ struct WorkHeader {
     int64_t dense_unique_tokens;
 };
 
+// A set of pages attended by the same queries (host-side intermediate of the builders).
+struct WorkSegment {
+    std::vector<int32_t> queries;
+    std::vector<int32_t> pages;
+    int64_t tokens = 0;
+    int partial_tokens = 0;  // valid tokens of the (single, last) partial page, 0 if none
+    int32_t q_off = 0, page_off = 0;
+    int owner = -1;          // the one request that ends in this segment and may extend it, or -1
+};
+
 class WorkList {
 public:
-    // Returns 0 or a negative error (bad index / bad argument).
+    // From a reference-format plan.  Returns 0 or a negative error (bad index / bad argument).
     int build(const PlanBucketView* buckets, int num_buckets, int batch, int hratio, int kv_heads,
               int page_size, int64_t num_cache_pages, const WorkOptions& opt);
+    // Straight from a built radix tree: every edge of the tree is a segment (its pages, attended
+    // by the requests that pass through it).  For every batch a block-id radix tree can express
+    // this is the list `build` derives from the tree's packed plan - the plan's boxes are
+    // regrouped into exactly these page sets - without packing the plan first, and it can be
+    // advanced in place afterwards.
+    int build_from_tree(const Tree& tree, int hratio, int kv_heads, int64_t num_cache_pages,
+                        const WorkOptions& opt);
+    // After Tree::plan_advance said yes: 1 if the growth fits the slack of the owners' segments
+    // (nothing is changed by the check), else 0.
+    int can_advance(const std::vector<Growth>& growth) const;
+    // Applies the growth to the blob and the header in place (item lengths, appended page ids).
+    void advance(const std::vector<Growth>& growth);
     const WorkHeader& header() const { return header_; }
     const std::vector<int32_t>& blob() const { return blob_; }
 
 private:
+    int finish(std::vector<WorkSegment>& segs, int batch, int hratio, int kv_heads, int page_size,
+               const WorkOptions& opt);
+    struct GrowSlot {
+        int32_t item = -1;       // streaming item (index in the blob) that holds the request's last tokens
+        int32_t next_page = 0;   // blob index of the first free slot behind the segment's page list
+        int32_t slack = 0;       // free slots left
+        int32_t last_tokens = 0; // valid tokens in the segment's last page
+    };
     WorkHeader header_{};
     std::vector<int32_t> blob_;
+    std::vector<GrowSlot> grow_;  // per request; empty for lists built from a plan
 };
 
 }  // namespace pat

@@ -142,7 +142,7 @@ def test_random_forests_with_ragged_segments(seed, dtype, hq, hk, d, native_lib)
     scale = 1.0 / math.sqrt(d)
     out, lse, tree = _run_tree(q, k, v, lens, tables, 16, hq // hk, hk, scale)
     hdr = tree.kernel_info.device_work(torch.device(DEV)).header
-    assert hdr.num_dense_items > hdr.num_dense_ctas > 0
+    assert hdr.num_dense_items > 0 and hdr.num_dense_ctas > 0
     ref_o, ref_l = O.paged_decode_attention(q, k, v, lens, tables, scale)
     _assert_close(out, lse, ref_o[:, 0], ref_l, dtype)
 
@@ -459,13 +459,16 @@ def test_merge_waits_for_a_dense_kernel_that_outlasts_the_streaming_kernel(nativ
 
     with torch.cuda.device(DEV):
         cur = torch.cuda.current_stream()
-        ws.fill_(0xFF)                                  # every float of the scratch is a NaN
+        def poison():
+            ws.fill_(0xFF)                              # every float of the scratch is a NaN
+            ws[:256].zero_()                            # (the control words at its head stay zero)
+        poison()
         want, want_lse = fresh()
         run(want, want_lse, 16, cur)
         torch.cuda.synchronize()
         assert torch.isfinite(want.float()).all()
         for _ in range(3):
-            ws.fill_(0xFF)
+            poison()
             got, got_lse = fresh()
             run(got, got_lse, 0, cur)
             torch.cuda.synchronize()
@@ -476,7 +479,7 @@ def test_merge_waits_for_a_dense_kernel_that_outlasts_the_streaming_kernel(nativ
         side.wait_stream(cur)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
-            ws.fill_(0xFF)
+            poison()
             run(got, got_lse, 0, torch.cuda.current_stream())
         for _ in range(3):
             got.fill_(float("nan"))
