@@ -146,6 +146,8 @@ typedef struct pat_work_header {
     int64_t dense_tokens;           /* same for dense items */
     int64_t stream_unique_tokens;   /* unique tokens of the segments the streaming kernel handles */
     int64_t dense_unique_tokens;
+    int32_t q_per_req;              /* query tokens per request the list was built for (1 = decode) */
+    int32_t limits_off;             /* per-(segment, query) visible-token limits, or -1 */
 } pat_work_header;
 
 /* Returns NULL and sets *status on failure. num_cache_pages > 0 enables a range check of page ids. */
@@ -156,6 +158,15 @@ pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int b
  * tree is one segment - its pages, attended by the requests that pass through it. */
 pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_t num_cache_pages,
                              const pat_work_options* options, int* status);
+/* Several query tokens per request (speculative decoding, a short chunk of prefill on top of a
+ * cached prefix; the reference sends such steps to vLLM's flash-attention instead and asserts
+ * max_decode_query_len <= 1, plugin/vllm/attention/backends/prefix_attn.py:877-904).  The tree is
+ * built from the requests' FULL lengths, the q_per_req new tokens included and already in the
+ * cache; position t of a request of length L attends to its first L - q_per_req + 1 + t tokens.
+ * In the resulting list a query is a (request, position) pair, id = request * q_per_req + position,
+ * and header.batch counts pairs.  Such a list cannot be advanced in place. */
+pat_work* pat_work_from_tree_multi(const pat_tree* t, int hratio, int kv_heads, int q_per_req,
+                                   int64_t num_cache_pages, const pat_work_options* options, int* status);
 /* One decode step later: the same requests, each with seq_lens[i] >= before and its table row
  * extended by the pages the new tokens need (the reference rebuilds tree, plan and tables from
  * scratch every step: prefix_attn/async_tree.py:23-30, and leaves them stale on multi-step
@@ -191,7 +202,7 @@ typedef struct pat_decode_args {
     const void* v_cache;
     void* out;            /* [batch, 1, num_q_heads, head_dim], same dtype as q */
     float* lse_out;       /* optional [batch, num_q_heads]: natural-log LSE of the scaled scores */
-    int64_t q_batch_stride, q_head_stride;
+    int64_t q_batch_stride, q_head_stride;   /* (query tokens per request > 1: see q_pos_stride below) */
     int64_t k_page_stride, k_row_stride, k_head_stride;
     int64_t v_page_stride, v_row_stride, v_head_stride;
     int64_t out_batch_stride, out_head_stride;
@@ -219,7 +230,12 @@ typedef struct pat_decode_args {
     int32_t* status_word;
     /* limit of every wait inside the kernels, in microseconds; 0 = one second */
     int32_t wait_limit_us;
-    int32_t reserved;
+    /* Query tokens per request; 0 or 1 = decode.  With T > 1, q and out are
+     * [batch, T, num_q_heads, head_dim] with the position strides below, `batch` is the number of
+     * requests, lse_out is [batch, T, num_q_heads], and the work list must come from
+     * pat_work_from_tree_multi with the same T. */
+    int32_t q_per_req;
+    int64_t q_pos_stride, out_pos_stride;
 } pat_decode_args;
 
 size_t pat_b200_workspace_bytes(const pat_work_header* work, int num_q_heads, int head_dim);

@@ -16,15 +16,18 @@ What it restates, in fp32 PyTorch on the host:
 * ``paged_decode_attention`` - the dense K/V gather from the paged cache that
   the reference's generator performs (``prefix_attn/utils.py:34-44``), done per
   request so that the large workloads fit in memory.
+* ``multi_position_attention`` - several query tokens per request, defined through one
+  ``attention_ref`` call per position (the reference has no such path of its own).
 * ``execute_plan`` - what a reference plan *means*: each box attends
   ``q_table[:num_seqs]`` x all their heads to the first ``kv_in_CTA`` tokens of
   its page list (``csrc/pat_fwd_kernel.h:25-299``, ``csrc/block_info.h:14-39``)
   and the per-query partials are combined by log-sum-exp
   (``csrc/pat_fwd_kernel.h:314-467``), with one slot per (box, query).
 
-Pinning: ``tests/test_oracle.py`` checks ``dense_attention`` against outputs of
-the real ``attention_ref`` frozen under ``tests/golden/attention_*.npz`` and,
-when the reference checkout is present, against ``attention_ref`` run live.
+Pinning: ``tests/test_oracle.py`` checks ``dense_attention`` and
+``multi_position_attention`` against outputs of the real ``attention_ref`` frozen under
+``tests/golden/attention_*.npz`` and, when the reference checkout is present, against
+``attention_ref`` run live.
 """
 from __future__ import annotations
 
@@ -90,6 +93,46 @@ def paged_decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         o, l = dense_attention(q[b:b + 1], kk, vv, None, softmax_scale)
         outs.append(o[0])
         lses.append(l[0, :, 0])
+    return torch.stack(outs), torch.stack(lses)
+
+
+def multi_position_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lens: Sequence[int],
+                             softmax_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Several query tokens per request, the last ``T`` tokens of each context: q [B,T,H,D],
+    k/v [B,S,Hkv,D], ``lens[b]`` = context length including those ``T`` tokens.  Position ``t``
+    attends to the first ``lens[b] - T + 1 + t`` keys.
+
+    The reference has no such path of its own (its serving backend hands steps with more than
+    one query token to another library, ``plugin/vllm/attention/backends/prefix_attn.py:877-904``)
+    and ``attention_ref`` has no causal argument (``test/utils.py:7-15``), so the definition is:
+    one single-token ``attention_ref`` call per position, with the padding mask cut at that
+    position's last visible key.  Returns ``(out [B,T,H,D], lse [B,T,H])``."""
+    B, T = q.shape[0], q.shape[1]
+    S = k.shape[1]
+    lens_t = torch.as_tensor(list(lens))
+    outs, lses = [], []
+    for t in range(T):
+        mask = torch.arange(S)[None, :] < (lens_t - T + 1 + t)[:, None]
+        o, l = dense_attention(q[:, t:t + 1], k, v, mask, softmax_scale)
+        outs.append(o)
+        lses.append(l[:, :, 0])
+    return torch.cat(outs, dim=1), torch.stack(lses, dim=1)
+
+
+def paged_multi_position_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                   seq_lens: Sequence[int], block_tables: Sequence[Sequence[int]],
+                                   softmax_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``multi_position_attention`` over a paged cache, request by request.
+    q [B,T,H,D]; returns ``(out [B,T,H,D] fp32, lse [B,T,H] fp32)``."""
+    page = k_cache.shape[1]
+    outs, lses = [], []
+    for b in range(q.shape[0]):
+        n_pages = -(-seq_lens[b] // page)
+        kk = gather_request_kv(k_cache, block_tables[b][:n_pages], seq_lens[b])[None]
+        vv = gather_request_kv(v_cache, block_tables[b][:n_pages], seq_lens[b])[None]
+        o, l = multi_position_attention(q[b:b + 1], kk, vv, [seq_lens[b]], softmax_scale)
+        outs.append(o[0])
+        lses.append(l[0])
     return torch.stack(outs), torch.stack(lses)
 
 

@@ -44,7 +44,8 @@ class WorkHeader(C.Structure):
                 ("dense_cta_off", C.c_int32), ("merge_indptr_off", C.c_int32), ("merge_entries_off", C.c_int32),
                 ("blob_words", C.c_int32), ("num_segments", C.c_int32), ("max_page_id", C.c_int32),
                 ("unique_tokens", C.c_int64), ("stream_tokens", C.c_int64), ("dense_tokens", C.c_int64),
-                ("stream_unique_tokens", C.c_int64), ("dense_unique_tokens", C.c_int64)]
+                ("stream_unique_tokens", C.c_int64), ("dense_unique_tokens", C.c_int64),
+                ("q_per_req", C.c_int32), ("limits_off", C.c_int32)]
 
 
 class DecodeArgs(C.Structure):
@@ -59,7 +60,8 @@ class DecodeArgs(C.Structure):
                 ("num_pages", C.c_int64), ("softmax_scale", C.c_float), ("flags", C.c_int32),
                 ("work_blob", C.c_void_p), ("work", WorkHeader),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("status_word", C.c_void_p), ("wait_limit_us", C.c_int32), ("reserved", C.c_int32)]
+                ("status_word", C.c_void_p), ("wait_limit_us", C.c_int32), ("q_per_req", C.c_int32),
+                ("q_pos_stride", C.c_int64), ("out_pos_stride", C.c_int64)]
 
 
 class AppendArgs(C.Structure):
@@ -96,6 +98,8 @@ SIGNATURES = {
                                      C.c_int64, C.POINTER(WorkOptions), C.POINTER(C.c_int)]),
     "pat_work_from_tree": (C.c_void_p, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.POINTER(WorkOptions),
                                         C.POINTER(C.c_int)]),
+    "pat_work_from_tree_multi": (C.c_void_p, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64,
+                                              C.POINTER(WorkOptions), C.POINTER(C.c_int)]),
     "pat_work_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "pat_tree_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "pat_work_destroy": (None, [C.c_void_p]),

@@ -219,13 +219,14 @@ class DeviceWork:
 
     @classmethod
     def from_tree(cls, tree_handle: int, hratio: int, kv_heads: int, device: torch.device,
-                  cfg: WorkConfig) -> "DeviceWork":
+                  cfg: WorkConfig, q_per_req: int = 1) -> "DeviceWork":
         lib = N.load()
         opts = cfg.as_struct()
         if opts.num_sms == 0 and device.type == "cuda":
             opts.num_sms = _sm_count(device)
         status = C.c_int(0)
-        handle = lib.pat_work_from_tree(tree_handle, hratio, kv_heads, 0, C.byref(opts), C.byref(status))
+        handle = lib.pat_work_from_tree_multi(tree_handle, hratio, kv_heads, int(q_per_req), 0, C.byref(opts),
+                                              C.byref(status))
         if not handle:
             raise RuntimeError(f"invalid plan: {N.strerror(status.value)}")
         return cls(handle, device, keep_native=True)
@@ -323,13 +324,15 @@ class KernelInfo:
             self.device_work(device)
             check_status(device, synchronize=False)     # a failed wait of an earlier step surfaces here
 
-    def device_work(self, device: torch.device, cfg: Optional[WorkConfig] = None) -> DeviceWork:
+    def device_work(self, device: torch.device, cfg: Optional[WorkConfig] = None, q_per_req: int = 1) -> DeviceWork:
+        """The work list on ``device`` (built and uploaded on first use).  ``q_per_req`` > 1: the list
+        for that many query tokens per request (the last tokens of each request's context)."""
         cfg = cfg or default_config()
-        key = (str(device), cfg.key())
+        key = (str(device), cfg.key()) if q_per_req == 1 else (str(device), cfg.key(), int(q_per_req))
         work = self._work.get(key)
         if work is None:
             o = self._owner
-            work = DeviceWork.from_tree(o._handle, o._hratio, o._kv_heads, device, cfg)
+            work = DeviceWork.from_tree(o._handle, o._hratio, o._kv_heads, device, cfg, q_per_req)
             self._work[key] = work
         return work
 
@@ -355,6 +358,8 @@ class PrefixTreeCPP:
         self._hratio = 1
         self._kv_heads = 8
         self._pack_args = None          # arguments of the last pack_schedule
+        self._deferred = None           # arguments of a pack that was put off
+        self._built = False
         self._packed = False            # the native tree holds a plan for its current state
         self._packed_once = False
 
@@ -405,6 +410,7 @@ class PrefixTreeCPP:
                                            offsets.ctypes.data, len(rows))
         if rc != 0:
             raise RuntimeError(f"build_radix_tree failed: {N.strerror(rc)}")
+        self._built = True
 
     def pack_schedule(self, MNWs: Optional[List[List[int]]] = None, HRatio: int = 1, kvHead: int = 8,
                       use_compute_model: bool = False) -> None:
@@ -414,8 +420,20 @@ class PrefixTreeCPP:
             ptr, n = arr.ctypes.data, arr.shape[0]
         else:
             arr, ptr, n = None, None, 0
-        rc = lib.pat_tree_pack(self._handle, ptr, n, int(HRatio), int(kvHead), int(bool(use_compute_model)))
         self._pack_args = (arr, int(HRatio), int(kvHead), int(bool(use_compute_model)))
+        if self.semantics == "cpp" and int(HRatio) > 0 and self._built and not self._packed_once:
+            # The C++ scheduler's pack cannot fail on a built tree, and the kernels here run from
+            # the work list, not from the plan: the first pack is put off until somebody reads
+            # ``kernel_info``.  (A second pack on the same tree accumulates, like the reference's,
+            # so it runs at once, after the first.)
+            self._hratio, self._kv_heads = int(HRatio), int(kvHead)
+            self._packed = False
+            self._packed_once = True
+            self._deferred = self._pack_args
+            self._kernel_info._invalidate()
+            return
+        self._ensure_packed_before_repack()
+        rc = lib.pat_tree_pack(self._handle, ptr, n, int(HRatio), int(kvHead), int(bool(use_compute_model)))
         if rc == -2:
             raise IndexError(N.strerror(rc))
         if rc == -3:
@@ -428,11 +446,22 @@ class PrefixTreeCPP:
         self._packed = self._packed_once = True
         self._kernel_info._invalidate()
 
+    def _ensure_packed_before_repack(self) -> None:
+        """A pack that was put off must have happened before the next one accumulates onto it."""
+        if self._packed_once and not self._packed and self._deferred is not None:
+            args, self._deferred = self._deferred, None
+            self._run_pack(args)
+
     def _ensure_packed(self) -> None:
-        """Packs again after an in-place advance dropped the plan (same arguments as last time)."""
+        """Runs a pack that was put off, or packs again after an in-place advance dropped the plan
+        (same arguments as last time)."""
         if self._packed or self._pack_args is None:
             return
-        arr, hratio, kv_heads, ucm = self._pack_args
+        self._deferred = None
+        self._run_pack(self._pack_args)
+
+    def _run_pack(self, args) -> None:
+        arr, hratio, kv_heads, ucm = args
         ptr, n = (arr.ctypes.data, arr.shape[0]) if arr is not None else (None, 0)
         rc = N.load().pat_tree_pack(self._handle, ptr, n, hratio, kv_heads, ucm)
         if rc != 0:
@@ -593,7 +622,7 @@ def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None,
     if cached is not None and cached[0] == key:
         a = cached[1]
     else:
-        B, _, H, D = q.shape
+        B, T, H, D = q.shape
         a = N.DecodeArgs()
         a.q, a.k_cache, a.v_cache, a.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
         a.lse_out = lse_out.data_ptr() if lse_out is not None else None
@@ -601,6 +630,7 @@ def _run(q, k_cache, v_cache, work: DeviceWork, scale: float, out, lse_out=None,
         a.k_page_stride, a.k_row_stride, a.k_head_stride = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
         a.v_page_stride, a.v_row_stride, a.v_head_stride = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
         a.out_batch_stride, a.out_head_stride = out.stride(0), out.stride(2)
+        a.q_per_req, a.q_pos_stride, a.out_pos_stride = T, q.stride(1), out.stride(1)
         a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = B, H, k_cache.shape[2], D
         a.page_size = k_cache.shape[1]
         a.dtype = _DTYPES[q.dtype]
@@ -635,7 +665,10 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
     ``PrefixTreeCPP`` whose ``kernel_info`` was moved to the GPU.
 
     ``q``/``out``: ``[batch, 1, heads, head_dim]``; caches: ``[pages, page_size, kv_heads,
-    head_dim]``; fp16 or bf16.  Extra keyword (not in the reference): ``lse_out``, a float32
+    head_dim]``; fp16 or bf16.  The tree form also takes ``[batch, T, heads, head_dim]`` with
+    ``T`` > 1 query tokens per request (speculative decoding, a short prefill chunk on a cached
+    prefix): the tree is then built from the full lengths, the ``T`` new tokens included, and
+    position ``t`` attends to the first ``len - T + 1 + t`` tokens of its request.  Extra keyword (not in the reference): ``lse_out``, a float32
     CUDA tensor ``[batch, heads]`` that receives the natural-log LSE of the scaled scores
     (the reference computes it, ``csrc/api.h:195``, but never returns it).
     """
@@ -682,14 +715,24 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
     ratio = H // Hkv
     _check(ratio in (1, 2, 4, 8), "only support QGA with hq/hkv = 1, 2, 4, 8 now.")
     _check(B > 0, "batch size must be positive")
-    _check(seqlen_q == 1, "q must have shape (batch_size, 1, n_heads, head_size)")
+    _check(seqlen_q >= 1, "q must have shape (batch_size, seqlen_q, n_heads, head_size)")
     _check(tuple(k_cache.shape) == (num_pages, page, Hkv, D), "kcache must have shape (num_blocks, page_block_size, n_heads_kv, head_size_og)")
     _check(tuple(v_cache.shape) == (num_pages, page, Hkv, D), "vcache must have shape (num_blocks, page_block_size, n_heads_kv, head_size_og)")
     _check(out.is_cuda and out.dtype == q.dtype and tuple(out.shape) == tuple(q.shape) and out.stride(-1) == 1,
            "out must be a CUDA tensor with the shape and dtype of q")
     if lse_out is not None:
+        want = (B, H) if seqlen_q == 1 else (B, seqlen_q, H)
         _check(lse_out.is_cuda and lse_out.dtype == torch.float32 and lse_out.is_contiguous()
-               and tuple(lse_out.shape) == (B, H), "lse_out must be a contiguous float32 CUDA tensor [batch, heads]")
+               and tuple(lse_out.shape) == want,
+               "lse_out must be a contiguous float32 CUDA tensor [batch, heads] ([batch, seqlen_q, heads])")
+    if seqlen_q > 1:
+        # Several query tokens per request (the reference sends these steps to another library,
+        # plugin/vllm/attention/backends/prefix_attn.py:877-904): the requests' lengths in the tree
+        # include the seqlen_q new tokens, which are already in the cache, and position t attends to
+        # the first len - seqlen_q + 1 + t tokens.  Tree form only.
+        _check(tree_form, "seqlen_q > 1 needs the tree form of the call")
+        _check(seqlen_q <= 64, "seqlen_q must be at most 64")
+        _check(q.stride(1) % 8 == 0 and out.stride(1) % 8 == 0, "q / out rows must be 16-byte aligned")
 
     if tree_form:
         tree = bound["tree"]
@@ -716,7 +759,7 @@ def prefix_attn_with_kvcache(*args, **kwargs) -> None:
     if tree_form:
         _check(tree._hratio == ratio, "the plan was packed for a different HRatio than q / k_cache imply")
         _check(tree.block_size == page, "the plan was built for a different page size than k_cache has")
-        work = info.device_work(q.device)
+        work = info.device_work(q.device, None, seqlen_q)
     else:
         qts, bts = list(bound["query_tables"]), list(bound["block_tables"])
         nss, rks, kvs = list(bound["num_seqs_per_CTAs"]), list(bound["CTA_ranks"]), list(bound["kv_in_CTAs"])

@@ -54,6 +54,8 @@ void copy_header(const pat::WorkHeader& h, pat_work_header* out) {
     out->dense_tokens = h.dense_tokens;
     out->stream_unique_tokens = h.stream_unique_tokens;
     out->dense_unique_tokens = h.dense_unique_tokens;
+    out->q_per_req = h.q_per_req;
+    out->limits_off = h.limits_off;
 }
 
 }  // namespace
@@ -207,13 +209,19 @@ pat_work* pat_work_create(const pat_plan_bucket* buckets, int num_buckets, int b
 
 pat_work* pat_work_from_tree(const pat_tree* t, int hratio, int kv_heads, int64_t num_cache_pages,
                              const pat_work_options* options, int* status) {
+    return pat_work_from_tree_multi(t, hratio, kv_heads, 1, num_cache_pages, options, status);
+}
+
+pat_work* pat_work_from_tree_multi(const pat_tree* t, int hratio, int kv_heads, int q_per_req,
+                                   int64_t num_cache_pages, const pat_work_options* options, int* status) {
     int dummy;
     if (!status) status = &dummy;
     if (!t) { *status = PAT_ERR_BAD_ARGUMENT; return nullptr; }
     pat_work* w = new (std::nothrow) pat_work();
     if (!w) { *status = PAT_ERR_NO_MEMORY; return nullptr; }
     try {
-        const int rc = w->list.build_from_tree(t->tree, hratio, kv_heads, num_cache_pages, to_options(options));
+        const int rc = w->list.build_from_tree(t->tree, hratio, kv_heads, num_cache_pages, to_options(options),
+                                               q_per_req);
         *status = map_work_error(rc);
         if (rc != 0) { delete w; return nullptr; }
         return w;

@@ -107,8 +107,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     p.part_lse = part_lse;
     p.queries = a.work_blob + a.work.queries_off;
     p.pages = a.work_blob + a.work.pages_off;
+    const int q_per_req = a.q_per_req > 1 ? a.q_per_req : 1;
+    const bool limits = a.work.limits_off >= 0;
+    p.limits = limits ? a.work_blob + a.work.limits_off : nullptr;
+    p.q_per_req = q_per_req;
     p.q_batch_stride = a.q_batch_stride;
     p.q_head_stride = a.q_head_stride;
+    p.q_pos_stride = q_per_req > 1 ? a.q_pos_stride : 0;
     p.kv_heads = a.num_kv_heads;
     p.hratio = a.work.hratio;
     p.num_q_heads = a.num_q_heads;
@@ -137,13 +142,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
     int32_t* sync = (overlap && merge) ? sync_words : nullptr;
     if (dense) {
         // shared segments on tcgen05 / TMEM: persistent CTAs, one per share of the dense work
-        static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
-        auto kern = dense_tc_kernel<T, D>;
+        static std::atomic<bool> configured[kMaxDevices][2];    // zero-initialised; set once per device
+        auto kern = limits ? dense_tc_kernel<T, D, true> : dense_tc_kernel<T, D, false>;
         constexpr int smem = TcSmem<D>::kRequest;
-        if (!configured[dev].load(std::memory_order_acquire)) {
+        if (!configured[dev][limits].load(std::memory_order_acquire)) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
                 return PAT_ERR_CUDA;
-            configured[dev].store(true, std::memory_order_release);
+            configured[dev][limits].store(true, std::memory_order_release);
         }
         AttnParams pd = p;
         pd.items = a.work_blob + a.work.items_off + static_cast<size_t>(a.work.num_stream_items) * 8;
@@ -156,13 +161,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         ++launches;
     }
     if (streaming) {
-        static std::atomic<bool> configured[kMaxDevices];    // zero-initialised; set once per device
-        auto kern = stream_kernel<T, D>;
+        static std::atomic<bool> configured[kMaxDevices][2];    // zero-initialised; set once per device
+        auto kern = limits ? stream_kernel<T, D, true> : stream_kernel<T, D, false>;
         constexpr int smem = stream_smem_bytes<D>();
-        if (!configured[dev].load(std::memory_order_acquire)) {
+        if (!configured[dev][limits].load(std::memory_order_acquire)) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
                 return PAT_ERR_CUDA;
-            configured[dev].store(true, std::memory_order_release);
+            configured[dev][limits].store(true, std::memory_order_release);
         }
         p.items = a.work_blob + a.work.items_off;
         p.num_items = a.work.num_stream_items;
@@ -194,11 +199,13 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         mp.lse_out = a.lse_out;
         mp.out_batch_stride = a.out_batch_stride;
         mp.out_head_stride = a.out_head_stride;
-        mp.batch = a.batch;
+        mp.out_pos_stride = q_per_req > 1 ? a.out_pos_stride : 0;
+        mp.q_per_req = q_per_req;
+        mp.batch = a.batch * q_per_req;
         mp.num_q_heads = a.num_q_heads;
         mp.kv_heads = a.num_kv_heads;
         mp.hratio = a.work.hratio;
-        const int total = a.batch * a.num_q_heads;
+        const int total = a.batch * q_per_req * a.num_q_heads;
         const int warps_per_cta = 8;
         merge_kernel<T, D><<<(total + warps_per_cta - 1) / warps_per_cta, warps_per_cta * 32, 0, stream>>>(mp);
         ++launches;
@@ -229,7 +236,12 @@ int pat_b200_decode(const pat_decode_args* args, void* stream_handle) {
     if (!a.q || !a.k_cache || !a.v_cache || !a.out || !a.work_blob) return PAT_ERR_BAD_ARGUMENT;
     if (a.batch <= 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0 || a.num_pages <= 0) return PAT_ERR_BAD_ARGUMENT;
     if (a.num_q_heads % a.num_kv_heads != 0) return PAT_ERR_BAD_ARGUMENT;
-    if (a.work.batch != a.batch || a.work.hratio != a.num_q_heads / a.num_kv_heads ||
+    const int positions = a.q_per_req > 1 ? a.q_per_req : 1;
+    if (a.work.q_per_req != positions || static_cast<int64_t>(a.work.batch) != static_cast<int64_t>(a.batch) * positions)
+        return PAT_ERR_BAD_PLAN;
+    if (positions > 1 && (a.q_pos_stride <= 0 || a.q_pos_stride % 8 != 0 || a.out_pos_stride <= 0 || a.out_pos_stride % 8 != 0))
+        return PAT_ERR_UNSUPPORTED;
+    if (a.work.hratio != a.num_q_heads / a.num_kv_heads ||
         a.work.page_size != a.page_size || a.work.kv_heads != a.num_kv_heads)
         return PAT_ERR_BAD_PLAN;
     if (a.work.max_page_id >= a.num_pages) return PAT_ERR_BAD_PLAN;

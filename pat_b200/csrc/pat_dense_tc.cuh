@@ -208,7 +208,9 @@ struct DenseTcParams {
 };
 
 // ------------------------------------------------------------------------------------
-template <typename T, int D>
+// kLimits: several query positions per request; a row may then see only the first part of an
+// item's tokens (AttnParams::limits), down to none of them.
+template <typename T, int D, bool kLimits>
 __global__ void __launch_bounds__(kTcThreads, 1)
 dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     // This CTA is running: a kernel launched as this one's programmatic dependent (the streaming
@@ -479,8 +481,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kvh = __ldg(it + 5);
         if (r >= nq * p.hratio) return nullptr;
         const int qi = r / p.hratio, gg = r - qi * p.hratio;
-        const T* q = static_cast<const T*>(p.q) + static_cast<int64_t>(__ldg(p.queries + q_off + qi)) * p.q_batch_stride +
-                     static_cast<int64_t>(kvh * p.hratio + gg) * p.q_head_stride;
+        const T* q = q_row_ptr<T>(p, __ldg(p.queries + q_off + qi), kvh * p.hratio + gg);
         return reinterpret_cast<const uint4*>(q) + half * (D / 16);
     };
     auto q_fetch = [&](const uint4* src, uint4 (&qv)[D / 16]) {
@@ -502,6 +503,9 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                   kvh = __ldg(it + 5);
         const int rows_valid = nq * p.hratio;
         const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
+        int row_limit = kv_len;             // tokens of this item that row r may see
+        if constexpr (kLimits)
+            row_limit = r < rows_valid ? visible_tokens(p, q_off + r / p.hratio, __ldg(it + 7), kv_len) : 0;
 
         // the first item's Q rows; those of every later item are written during the last tile of the
         // item before it (below)
@@ -535,10 +539,11 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             float sc[CH];
             tmem_ld_f<CH>(lane_addr + s * kTcTile + half * CH, sc);
             const int valid = min(kTcTile, kv_len - j * kTcTile);
-            if (valid < kTcTile) {
+            const int row_valid = kLimits ? min(valid, row_limit - j * kTcTile) : valid;
+            if (row_valid < kTcTile) {
 #pragma unroll
                 for (int i = 0; i < CH; ++i)
-                    if (half * CH + i >= valid) sc[i] = -INFINITY;
+                    if (half * CH + i >= row_valid) sc[i] = -INFINITY;
             }
             float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
 #pragma unroll
@@ -549,7 +554,10 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             float* xbuf = xch + (t & 1) * 256;
             xbuf[half * 128 + r] = fmaxf(mx0, mx1);
             pair_sync();
-            const float mx = fmaxf(fmaxf(mx0, mx1), xbuf[(half ^ 1) * 128 + r]);
+            float mx = fmaxf(fmaxf(mx0, mx1), xbuf[(half ^ 1) * 128 + r]);
+            // A row that sees nothing of this tile has mx = -inf; a large finite floor keeps the
+            // offsets finite (exp2(-inf - finite) = 0) and gives way to the first real score.
+            if constexpr (kLimits) mx = fmaxf(mx, -1e30f);
             const bool raise = (j == 0) || (mx * c > m_used * c + kTcLazyLog2);
             if (j > 0 && __any_sync(kFullMask, raise)) {
                 ensure_o(t);            // O may only be touched once every earlier P V has completed
@@ -619,7 +627,7 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                 const int qi = r / p.hratio, gg = r - qi * p.hratio;
                 slot = static_cast<size_t>(entry_base + qi) * p.hratio + gg;
             }
-            const float inv = 1.f / l_row;
+            const float inv = (!kLimits || l_row > 0.f) ? 1.f / l_row : 0.f;    // a row that saw nothing
             float ov[OC];
             tmem_ld_f<OC>(tmem_o, ov);
             tc_fence_before();
@@ -635,7 +643,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                                    "f"(ov[8 * i + 3] * inv), "f"(ov[8 * i + 4] * inv), "f"(ov[8 * i + 5] * inv),
                                    "f"(ov[8 * i + 6] * inv), "f"(ov[8 * i + 7] * inv)
                                  : "memory");
-                if (half == 0) p.part_lse[slot] = m_used * p.scale + logf(l_row);
+                if (half == 0)
+                    p.part_lse[slot] = (!kLimits || l_row > 0.f) ? m_used * p.scale + logf(l_row) : -INFINITY;
             }
         }
     }

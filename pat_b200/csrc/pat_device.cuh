@@ -149,10 +149,13 @@ template <int D> struct TileGeom {
     static constexpr int kNTilesO = D / 8;
 };
 
-template <typename T, int D, int NSUB>
+// valid0 / valid1: tokens of the tile the thread's first / second row may attend to (the same
+// number unless kLimits: several query positions per request see different ends of the context;
+// a row may then see nothing of a tile, or of all tiles so far, which the -inf handling covers).
+template <typename T, int D, int NSUB, bool kLimits = false>
 __device__ __forceinline__ void warp_attend_tile(const uint32_t (&qf)[D / 16][4], float (&o)[D / 8][4],
                                                  float (&m)[2], float (&l)[2], uint32_t stage_addr,
-                                                 int valid_tokens, float c, int lane) {
+                                                 int valid0, int valid1, float c, int lane) {
     using G = TileGeom<D>;
     float s[2 * NSUB][4];
 #pragma unroll
@@ -177,14 +180,16 @@ __device__ __forceinline__ void warp_attend_tile(const uint32_t (&qf)[D / 16][4]
         }
     }
 
-    // mask the tail of the last tile
-    if (valid_tokens < 16 * NSUB) {
+    // mask the tail of the last tile (and, with limits, what a row must not see)
+    if (valid0 < 16 * NSUB || (kLimits && valid1 < 16 * NSUB)) {
         const int col0 = (lane & 3) << 1;
 #pragma unroll
         for (int i = 0; i < 2 * NSUB; ++i) {
             const int col = i * 8 + col0;
-            if (col >= valid_tokens) { s[i][0] = -INFINITY; s[i][2] = -INFINITY; }
-            if (col + 1 >= valid_tokens) { s[i][1] = -INFINITY; s[i][3] = -INFINITY; }
+            if (col >= valid0) s[i][0] = -INFINITY;
+            if (col + 1 >= valid0) s[i][1] = -INFINITY;
+            if (col >= valid1) s[i][2] = -INFINITY;
+            if (col + 1 >= valid1) s[i][3] = -INFINITY;
         }
     }
 
@@ -202,7 +207,9 @@ __device__ __forceinline__ void warp_attend_tile(const uint32_t (&qf)[D / 16][4]
     const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
     const bool changed = (mn0 != m[0]) || (mn1 != m[1]);
     if (__any_sync(kFullMask, changed)) {
-        const float a0 = fast_exp2((m[0] - mn0) * c), a1 = fast_exp2((m[1] - mn1) * c);
+        // (a row that has seen nothing yet has m = -inf: its l and o are 0 and stay 0)
+        const float a0 = (kLimits && m[0] == -INFINITY) ? 0.f : fast_exp2((m[0] - mn0) * c);
+        const float a1 = (kLimits && m[1] == -INFINITY) ? 0.f : fast_exp2((m[1] - mn1) * c);
         l[0] *= a0;
         l[1] *= a1;
 #pragma unroll
@@ -213,7 +220,9 @@ __device__ __forceinline__ void warp_attend_tile(const uint32_t (&qf)[D / 16][4]
     }
     m[0] = mn0;
     m[1] = mn1;
-    const float b0 = mn0 * c, b1 = mn1 * c;
+    // a row whose maximum is still -inf has only masked scores: any finite offset gives exp2(-inf) = 0
+    const float b0 = (kLimits && mn0 == -INFINITY) ? 0.f : mn0 * c;
+    const float b1 = (kLimits && mn1 == -INFINITY) ? 0.f : mn1 * c;
     uint32_t pa[NSUB][4];
 #pragma unroll
     for (int u = 0; u < NSUB; ++u) {

@@ -29,7 +29,11 @@ struct AttnParams {
     const int32_t* items;     // WorkItem[...]
     const int32_t* queries;
     const int32_t* pages;
-    int64_t q_batch_stride, q_head_stride;
+    // Several query tokens per request: a query id is request * q_per_req + position, and
+    // `limits` (parallel to `queries`, or null) holds how many tokens of its segment each query sees.
+    const int32_t* limits;
+    int64_t q_batch_stride, q_head_stride, q_pos_stride;
+    int q_per_req;
     int num_items;
     int kv_heads;
     int hratio;
@@ -49,23 +53,35 @@ template <int D> constexpr int stream_smem_bytes() {
     return kStreamWarps * kStreamStages * TileGeom<D>::kSubBytes + 1024;
 }
 
+// Address of the Q row of query id `vq` (request * q_per_req + position) and query head `head`.
+template <typename T>
+__device__ __forceinline__ const T* q_row_ptr(const AttnParams& p, int vq, int head) {
+    const int req = p.q_per_req == 1 ? vq : vq / p.q_per_req;
+    const int pos = vq - req * p.q_per_req;
+    return static_cast<const T*>(p.q) + static_cast<int64_t>(req) * p.q_batch_stride +
+           static_cast<int64_t>(pos) * p.q_pos_stride + static_cast<int64_t>(head) * p.q_head_stride;
+}
+
+// Tokens of an item (first token tok_lo of its segment, kv_len tokens) that query slot `slot`
+// of the query section may see.
+__device__ __forceinline__ int visible_tokens(const AttnParams& p, int slot, int tok_lo, int kv_len) {
+    return max(0, min(kv_len, __ldg(p.limits + slot) - tok_lo));
+}
+
 // Q rows of one 16-row tile straight into mma A fragments.
 template <typename T, int D>
 __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], const AttnParams& p, const int32_t* qids,
                                              int row_base, int rows_valid, int kvh, int lane) {
-    const T* q = static_cast<const T*>(p.q);
     const int r0 = row_base + (lane >> 2), r1 = r0 + 8;
     const T* p0 = nullptr;
     const T* p1 = nullptr;
     if (r0 < rows_valid) {
         const int qi = r0 / p.hratio, g = r0 - qi * p.hratio;
-        p0 = q + static_cast<int64_t>(__ldg(qids + qi)) * p.q_batch_stride +
-             static_cast<int64_t>(kvh * p.hratio + g) * p.q_head_stride;
+        p0 = q_row_ptr<T>(p, __ldg(qids + qi), kvh * p.hratio + g);
     }
     if (r1 < rows_valid) {
         const int qi = r1 / p.hratio, g = r1 - qi * p.hratio;
-        p1 = q + static_cast<int64_t>(__ldg(qids + qi)) * p.q_batch_stride +
-             static_cast<int64_t>(kvh * p.hratio + g) * p.q_head_stride;
+        p1 = q_row_ptr<T>(p, __ldg(qids + qi), kvh * p.hratio + g);
     }
     const int col = (lane & 3) << 1;
 #pragma unroll
@@ -80,7 +96,7 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], const At
 // ------------------------------------------------------------------------------
 // Streaming kernel
 // ------------------------------------------------------------------------------
-template <typename T, int D>
+template <typename T, int D, bool kLimits>
 __global__ void __launch_bounds__(kStreamWarps * 32)
 stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     using G = TileGeom<D>;
@@ -98,6 +114,14 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
     const int q_off = __ldg(it + 0), nq = __ldg(it + 1), page_off = __ldg(it + 2), kv_len = __ldg(it + 3),
               entry_base = __ldg(it + 4);
     const int rows_valid = nq * p.hratio;
+    // tokens of this item the thread's two rows (lane / 4 and lane / 4 + 8) may see
+    int lim0 = kv_len, lim1 = kv_len;
+    if constexpr (kLimits) {
+        const int tok_lo = __ldg(it + 7);
+        const int r0 = lane >> 2, r1 = r0 + 8;
+        lim0 = r0 < rows_valid ? visible_tokens(p, q_off + r0 / p.hratio, tok_lo, kv_len) : 0;
+        lim1 = r1 < rows_valid ? visible_tokens(p, q_off + r1 / p.hratio, tok_lo, kv_len) : 0;
+    }
 
     if (tid == 0) {
         sm_abort = 0;
@@ -171,7 +195,9 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
             zero_v_tail<D>(my_stage + s * G::kSubBytes, 0, valid, lane);
             __syncwarp();
         }
-        warp_attend_tile<T, D, 1>(qf, o, m, l, my_stage_addr + s * G::kSubBytes, valid, p.scale_log2, lane);
+        warp_attend_tile<T, D, 1, kLimits>(qf, o, m, l, my_stage_addr + s * G::kSubBytes,
+                                            kLimits ? min(valid, lim0 - (t << 4)) : valid,
+                                            kLimits ? min(valid, lim1 - (t << 4)) : valid, p.scale_log2, lane);
         __syncwarp();
         const int jn = j + S;
         if ((jn & 31) == 0) { ids_cur = ids_next; ids_next = fetch_ids(jn + 32); }
@@ -230,12 +256,12 @@ stream_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
                 const float4 x = *reinterpret_cast<const float4*>(scratch + (static_cast<size_t>(w) * 16 + row) * kRowStride + v4 * 4);
                 acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
             }
-            const float inv = 1.f / L;
+            const float inv = (!kLimits || L > 0.f) ? 1.f / L : 0.f;    // a row that sees none of the item's tokens
             const int qi = row / p.hratio, gg = row - qi * p.hratio;
             // entry of (query qi, KV head kvh) = entry_base + qi * kv_heads + kvh; hratio rows per entry
             const size_t slot = (static_cast<size_t>(entry_base) + static_cast<size_t>(qi) * p.kv_heads + kvh) * p.hratio + gg;
             *reinterpret_cast<float4*>(p.part_o + slot * D + v4 * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-            if (v4 == 0) p.part_lse[slot] = g * p.scale + logf(L);
+            if (v4 == 0) p.part_lse[slot] = (!kLimits || L > 0.f) ? g * p.scale + logf(L) : -INFINITY;
         }
     }
 }
@@ -250,8 +276,9 @@ struct MergeParams {
     const int32_t* entries;
     void* out;
     float* lse_out;           // optional [batch, H]
-    int64_t out_batch_stride, out_head_stride;
-    int batch, num_q_heads, kv_heads, hratio;
+    int64_t out_batch_stride, out_head_stride, out_pos_stride;
+    int batch, num_q_heads, kv_heads, hratio;      // batch counts queries: requests x q_per_req
+    int q_per_req;
     // Control words at the head of the workspace, or null.  Set when the dense kernel ran beside
     // the streaming kernel: this kernel is then ordered after the streaming kernel only, and waits
     // here for the word the last dense CTA sets (see dense_tc_kernel).
@@ -365,7 +392,9 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
         }
     }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-    T* dst = static_cast<T*>(p.out) + static_cast<int64_t>(b) * p.out_batch_stride +
+    const int req = p.q_per_req == 1 ? b : b / p.q_per_req;
+    T* dst = static_cast<T*>(p.out) + static_cast<int64_t>(req) * p.out_batch_stride +
+             static_cast<int64_t>(b - req * p.q_per_req) * p.out_pos_stride +
              static_cast<int64_t>(h) * p.out_head_stride + lane * kPer;
     if constexpr (kPer == 4) {
         uint2 v;

@@ -91,7 +91,7 @@ void Tree::insert(int seq, int seq_len, const int* pages, int left) {
             shared = lo + 1;
         } else {
             const int limit = std::min(edge_n, left);
-            while (shared < limit && pages[shared] == edge[shared]) ++shared;
+            shared = static_cast<int>(std::mismatch(pages, pages + limit, edge).first - pages);
         }
         if (shared == edge_n) {
             nodes_[child].s_value += 1;

@@ -206,15 +206,29 @@ int WorkList::build(const PlanBucketView* buckets, int num_buckets, int batch, i
 }
 
 int WorkList::build_from_tree(const Tree& tree, int hratio, int kv_heads, int64_t num_cache_pages,
-                              const WorkOptions& opt) {
+                              const WorkOptions& opt, int q_per_req) {
     header_ = WorkHeader{};
     blob_.clear();
     grow_.clear();
     const int batch = tree.batch(), page_size = tree.block_size();
     if (batch <= 0 || hratio < 1 || hratio > 16 || kv_heads < 1 || page_size < 16 || page_size % 16 != 0 ||
-        opt.stream_rows < hratio)
+        opt.stream_rows < hratio || q_per_req < 1 || q_per_req > 64)
         return -1;
     const std::vector<TreeNode>& nodes = tree.nodes();
+    const int T = q_per_req;
+    // tokens on the path from the root to each node's parent (nodes are created parents first,
+    // except that a split inserts the new parent after its child: walk up instead of indexing)
+    std::vector<int64_t> start(nodes.size(), -1);
+    auto start_of = [&](int n) {
+        // iterative: climb to the first node whose start is known, then fill back down
+        std::vector<int> chain;
+        int at = n;
+        while (at > 0 && start[at] < 0) { chain.push_back(at); at = nodes[at].parent; }
+        int64_t s = at > 0 ? start[at] + nodes[at].length : 0;
+        // `s` is the start of the children of `at`; chain holds the path downwards in reverse
+        for (auto it = chain.rbegin(); it != chain.rend(); ++it) { start[*it] = s; s += nodes[*it].length; }
+        return start[n];
+    };
     std::vector<Segment> segs;
     segs.reserve(nodes.size());
     for (size_t n = 1; n < nodes.size(); ++n) {
@@ -222,19 +236,38 @@ int WorkList::build_from_tree(const Tree& tree, int hratio, int kv_heads, int64_
         if (node.length <= 0 || node.seq_indices.empty() || !node.pages) continue;
         const int np = ceil_div(node.length, page_size);
         Segment sg;
-        sg.queries.assign(node.seq_indices.begin(), node.seq_indices.end());
-        for (int32_t q : sg.queries)
+        for (int32_t q : node.seq_indices)
             if (q < 0 || q >= batch) return -3;
+        if (T == 1) {
+            sg.queries.assign(node.seq_indices.begin(), node.seq_indices.end());
+        } else {
+            // one query per (request, position); position t of a request of length L sees the first
+            // L - T + 1 + t tokens of the request, hence this many of the segment's
+            const int64_t s0 = start_of(static_cast<int>(n));
+            bool all_full = true;
+            for (int32_t q : node.seq_indices) {
+                for (int t = 0; t < T; ++t) {
+                    const int64_t visible = static_cast<int64_t>(tree.seq_len(q)) - T + 1 + t - s0;
+                    const int32_t lim = static_cast<int32_t>(std::max<int64_t>(0, std::min<int64_t>(visible, node.length)));
+                    sg.queries.push_back(q * T + t);
+                    sg.limits.push_back(lim);
+                    all_full = all_full && lim == node.length;
+                }
+            }
+            if (all_full) sg.limits.clear();
+        }
         sg.pages.assign(node.pages, node.pages + np);
         for (int32_t pg : sg.pages)
             if (pg < 0 || (num_cache_pages > 0 && pg >= num_cache_pages)) return -4;
         sg.tokens = node.length;
         sg.partial_tokens = node.length % page_size;
-        const int only = sg.queries.size() == 1 ? sg.queries[0] : -1;
+        const int only = (T == 1 && sg.queries.size() == 1) ? sg.queries[0] : -1;
         if (only >= 0 && node.children.empty() && tree.leaf_of(only) == static_cast<int>(n)) sg.owner = only;
         segs.push_back(std::move(sg));
     }
-    return finish(segs, batch, hratio, kv_heads, page_size, opt);
+    const int rc = finish(segs, batch * T, hratio, kv_heads, page_size, opt);
+    header_.q_per_req = T;
+    return rc;
 }
 
 int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_heads, int page_size,
@@ -262,10 +295,16 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     want = std::min<int64_t>(want, std::max(opt.chunk_tokens_max, page_size));
     const int stream_chunk = static_cast<int>(want);
 
-    std::vector<int32_t> queries_sec, pages_sec;
+    std::vector<int32_t> queries_sec, pages_sec, limits_sec;
+    bool any_limits = false;
+    for (const Segment& sg : segs) any_limits = any_limits || !sg.limits.empty();
     for (Segment& sg : segs) {
         sg.q_off = static_cast<int32_t>(queries_sec.size());
         queries_sec.insert(queries_sec.end(), sg.queries.begin(), sg.queries.end());
+        if (any_limits) {
+            if (sg.limits.empty()) limits_sec.insert(limits_sec.end(), sg.queries.size(), static_cast<int32_t>(sg.tokens));
+            else limits_sec.insert(limits_sec.end(), sg.limits.begin(), sg.limits.end());
+        }
         sg.page_off = static_cast<int32_t>(pages_sec.size());
         pages_sec.insert(pages_sec.end(), sg.pages.begin(), sg.pages.end());
         // room to grow in place; a dense segment is never extended (its owner would need >= 17 rows)
@@ -294,11 +333,11 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
                 it.page_off = sg.page_off + p0;
                 it.kv_len = kv;
                 it.entry_base = num_entries;
-                it.kv_head = -1;
+                // the item that holds the last tokens of a segment one request owns is remembered
+                // (through the sort below, as a head number <= -2) as the item WorkList::advance extends
+                it.kv_head = (sg.owner >= 0 && p1 == np) ? -(sg.owner + 2) : -1;
                 it.cost = kv;
-                // the item that holds the last tokens of a segment one request owns: remembered
-                // (through the sort below) as the item WorkList::advance extends
-                it.reserved = (sg.owner >= 0 && p1 == np) ? sg.owner + 1 : 0;
+                it.tok_lo = static_cast<int32_t>(tok_lo);
                 num_entries += it.nq * kv_heads;
                 for (int i = 0; i < it.nq; ++i)
                     for (int h = 0; h < kv_heads; ++h)
@@ -316,8 +355,7 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
         grow_.assign(static_cast<size_t>(batch), GrowSlot{});
         for (size_t i = 0; i < stream_items.size(); ++i) {
             WorkItem& it = stream_items[i];
-            if (it.reserved > 0) grow_[it.reserved - 1].item = static_cast<int32_t>(i);
-            it.reserved = 0;
+            if (it.kv_head <= -2) grow_[-it.kv_head - 2].item = static_cast<int32_t>(i);
         }
         for (const Segment& sg : segs) {
             if (sg.owner < 0 || is_dense(sg)) continue;
@@ -327,6 +365,7 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
             g.last_tokens = sg.partial_tokens > 0 ? sg.partial_tokens : page_size;
         }
     }
+    for (WorkItem& it : stream_items) it.kv_head = -1;
 
     // ---- 6. dense items: equal token shares per persistent CTA ------------------
     // The token ranges of the dense segments are laid end to end and cut into `shares` parts of
@@ -457,6 +496,7 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
                             it.entry_base = num_entries;
                             it.kv_head = h;
                             it.cost = static_cast<int32_t>(pc.take);
+                            it.tok_lo = static_cast<int32_t>(pc.pos);
                             num_entries += it.nq;
                             for (int i = 0; i < it.nq; ++i)
                                 per_list[static_cast<size_t>(sg->queries[q0 + i]) * kv_heads + h] += 1;
@@ -494,7 +534,8 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     auto align8 = [](size_t v) { return (v + 7) / 8 * 8; };
     const size_t items_off = 0;
     const size_t queries_off = align8(items_off + n_items * 8);
-    const size_t pages_off = align8(queries_off + queries_sec.size());
+    const size_t limits_off = align8(queries_off + queries_sec.size());
+    const size_t pages_off = align8(limits_off + limits_sec.size());
     const size_t cta_off = align8(pages_off + pages_sec.size());
     const size_t indptr_off = align8(cta_off + cta_begin.size());
     const size_t entries_off = align8(indptr_off + indptr.size());
@@ -506,6 +547,7 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
         std::memcpy(blob_.data() + items_off + stream_items.size() * 8, dense_items.data(),
                     dense_items.size() * sizeof(WorkItem));
     std::copy(queries_sec.begin(), queries_sec.end(), blob_.begin() + queries_off);
+    std::copy(limits_sec.begin(), limits_sec.end(), blob_.begin() + limits_off);
     std::copy(pages_sec.begin(), pages_sec.end(), blob_.begin() + pages_off);
     std::copy(cta_begin.begin(), cta_begin.end(), blob_.begin() + cta_off);
     std::copy(indptr.begin(), indptr.end(), blob_.begin() + indptr_off);
@@ -531,12 +573,15 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     header_.max_page_id = -1;
     for (int32_t pg : pages_sec) header_.max_page_id = std::max(header_.max_page_id, pg);
     header_.unique_tokens = unique_tokens;
+    header_.q_per_req = 1;
+    header_.limits_off = any_limits ? static_cast<int32_t>(limits_off) : -1;
     for (GrowSlot& g : grow_)
         if (g.item >= 0) g.next_page += static_cast<int32_t>(pages_off);
     return 0;
 }
 
 int WorkList::can_advance(const std::vector<Growth>& growth) const {
+    if (header_.q_per_req != 1) return 0;       // per-position limits are not patched in place
     if (grow_.empty()) return growth.empty() ? 1 : 0;
     for (const Growth& gr : growth) {
         if (gr.seq < 0 || gr.seq >= static_cast<int>(grow_.size())) return 0;

@@ -71,7 +71,7 @@ struct WorkItem {
                          // dense:     entry of query i            = entry_base + i
     int32_t kv_head;     // dense items: the KV head; streaming items: -1 (run for every head)
     int32_t cost;        // tokens (ordering key)
-    int32_t reserved;
+    int32_t tok_lo;      // first token of the item inside its segment (used with the per-query limits)
 };
 static_assert(sizeof(WorkItem) == 32, "device layout");
 
@@ -99,6 +99,13 @@ struct WorkHeader {
     int64_t dense_tokens;         // same for dense items
     int64_t stream_unique_tokens; // unique tokens of the segments the streaming kernel handles
     int64_t dense_unique_tokens;
+    // Several query tokens per request (seqlen_q = q_per_req > 1): a "query" of the list is then the
+    // pair (request, position), id = request * q_per_req + position, `batch` counts those pairs,
+    // and the section at limits_off (parallel to the query section) holds, per (segment, query),
+    // how many of the segment's tokens that position may see.  limits_off = -1 when every query
+    // sees all tokens of its segments (q_per_req = 1).
+    int32_t q_per_req;
+    int32_t limits_off;
 };
 
 // A set of pages attended by the same queries (host-side intermediate of the builders).
@@ -109,6 +116,7 @@ struct WorkSegment {
     int partial_tokens = 0;  // valid tokens of the (single, last) partial page, 0 if none
     int32_t q_off = 0, page_off = 0;
     int owner = -1;          // the one request that ends in this segment and may extend it, or -1
+    std::vector<int32_t> limits;  // per query: visible tokens of this segment; empty = all of them
 };
 
 class WorkList {
@@ -121,8 +129,10 @@ public:
     // this is the list `build` derives from the tree's packed plan - the plan's boxes are
     // regrouped into exactly these page sets - without packing the plan first, and it can be
     // advanced in place afterwards.
+    // q_per_req > 1: every request carries that many query tokens, the last q_per_req tokens of
+    // its context; position t attends to the first seq_len - q_per_req + 1 + t tokens.
     int build_from_tree(const Tree& tree, int hratio, int kv_heads, int64_t num_cache_pages,
-                        const WorkOptions& opt);
+                        const WorkOptions& opt, int q_per_req = 1);
     // After Tree::plan_advance said yes: 1 if the growth fits the slack of the owners' segments
     // (nothing is changed by the check), else 0.
     int can_advance(const std::vector<Growth>& growth) const;

@@ -17,6 +17,8 @@ Writes, next to this file:
   produce for seeded calls (checks this repository's mirrors of them);
 * ``attention_ref.npz`` - inputs' seeds and outputs of the reference's
   ``attention_ref`` (``test/utils.py``) on small dense problems.
+* ``attention_ref_positions.npz`` - the same function called once per query position
+  (several query tokens per request, each seeing one more key than the one before).
 
 Nothing here runs in the product; the tests only read the files.
 """
@@ -171,6 +173,26 @@ def main():
         att[f"probs_rowsum{seed}"] = probs.sum(-1).numpy()
         att[f"spec{seed}"] = np.array([seed, b, t_, h, hk, d, s, {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[dt]])
     np.savez_compressed(os.path.join(HERE, "attention_ref.npz"), **att)
+
+    # ---- several query positions per request: the reference's attention_ref has no causal
+    # argument, so position t of a request with context L is ONE single-token call whose padding
+    # mask keeps the first L - T + 1 + t keys; the outputs are stacked along the position axis
+    multi = {}
+    for seed, b, t_, h, hk, d, s in [(10, 3, 2, 8, 2, 64, 70), (11, 2, 4, 16, 2, 128, 133), (12, 2, 8, 8, 1, 64, 40)]:
+        gen = torch.Generator().manual_seed(seed)
+        q = (torch.randn(b, t_, h, d, generator=gen) * 0.5).bfloat16().float()
+        k = (torch.randn(b, s, hk, d, generator=gen) * 0.5).bfloat16().float()
+        v = (torch.randn(b, s, hk, d, generator=gen) * 0.5).bfloat16().float()
+        lens = torch.randint(t_, s + 1, (b,), generator=gen)
+        outs = []
+        for t in range(t_):
+            mask = torch.arange(s)[None, :] < (lens - t_ + 1 + t)[:, None]
+            o, _ = attention_ref(q[:, t:t + 1], k, v, None, mask)
+            outs.append(o)
+        multi[f"out{seed}"] = torch.cat(outs, dim=1).numpy()
+        multi[f"spec{seed}"] = np.array([seed, b, t_, h, hk, d, s])
+        multi[f"lens{seed}"] = lens.numpy()
+    np.savez_compressed(os.path.join(HERE, "attention_ref_positions.npz"), **multi)
 
     for name, obj in (("plans_py.json", plans_py), ("plans_cpp.json", plans_cpp),
                       ("legacy_py.json", legacy), ("generators.json", gens)):

@@ -535,3 +535,75 @@ def test_default_status_word_and_upload_ordering_on_a_side_stream(native_lib):
     P.check_status(DEV)
     assert P.status_word(DEV)[0].item() == 0
     _assert_close(out.float().cpu()[:, 0], lse.cpu(), ref_o[:, 0], ref_l, torch_dtype(w.dtype))
+
+
+# ---------------------------------------------------------------------------------------------
+# Several query tokens per request (speculative decoding, a prefill chunk on a cached prefix)
+# ---------------------------------------------------------------------------------------------
+def _run_positions(q, k, v, lens, tables, page, hratio, hk, scale):
+    tree = PrefixTreeCPP(page)
+    tree.build_radix_tree(list(lens), _padded(tables))
+    tree.pack_schedule(None, hratio, hk)
+    tree.kernel_info.to_gpu(torch.device(DEV))
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out = torch.full_like(qd, float("nan"))
+    lse = torch.full(tuple(q.shape[:3]), float("nan"), device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    prefix_attn_with_kvcache(qd, kd, vd, tree, scale, out, lse_out=lse, _status=status)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    return out.float().cpu(), lse.cpu(), tree
+
+
+@pytest.mark.parametrize("cfg,factor", [(1, 4), (3, 2)])
+@pytest.mark.parametrize("T", [2, 4, 8])
+def test_several_query_tokens_per_request(cfg, factor, T, native_lib):
+    """q [B, T, H, D]: the T query tokens are the last T tokens of every context (already in the
+    cache); position t attends to the first len - T + 1 + t tokens.  The oracle is one dense
+    attention per (request, position), pinned against the reference's attention_ref."""
+    w = scaled_down(cfg, factor)
+    _, k, v = make_values(w)
+    dtype = torch_dtype(w.dtype)
+    g = torch.Generator().manual_seed(100 * cfg + T)
+    q = (torch.randn(w.batch, T, w.num_q_heads, w.head_dim, generator=g) * 0.5).to(dtype)
+    scale = 1.0 / math.sqrt(w.head_dim)
+    out, lse, tree = _run_positions(q, k, v, w.seq_lens, w.block_tables, w.page_size, w.group, w.num_kv_heads, scale)
+    hdr = tree.kernel_info.device_work(torch.device(DEV), None, T).header
+    assert hdr.q_per_req == T and hdr.batch == w.batch * T and hdr.limits_off >= 0
+    ref_o, ref_l = O.paged_multi_position_attention(q, k, v, w.seq_lens, w.block_tables, scale)
+    _assert_close(out, lse, ref_o, ref_l, dtype)
+    # the last position is ordinary decode attention: the T = 1 call on the same tree agrees
+    one, one_lse, _ = _run_tree(q[:, -1:].contiguous(), k, v, w.seq_lens, w.block_tables, w.page_size, w.group,
+                                w.num_kv_heads, scale)
+    assert (out[:, -1] - one).abs().max().item() <= TOL[dtype]
+    assert (lse[:, -1] - one_lse).abs().max().item() <= 1e-3
+
+
+@pytest.mark.parametrize("seed,T,dtype,hq,hk,d", [(2, 3, torch.float16, 16, 2, 64), (4, 8, torch.bfloat16, 32, 4, 128),
+                                                  (5, 2, torch.bfloat16, 8, 8, 128), (10, 5, torch.float16, 32, 4, 64)])
+def test_query_positions_that_reach_back_into_shared_segments(seed, T, dtype, hq, hk, d, native_lib):
+    """Random forests with tails of 1..299 tokens: with T up to 8 the first positions of a short
+    tail see only part (or nothing) of the request's own last segment, in streaming and in dense
+    items, and q / out are passed as strided views."""
+    lens, tables, pages = _random_forest(seed, cap=120)
+    lens = [max(l, T) for l in lens]
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    qfull = (torch.randn(B, T + 1, hq, d, generator=g) * 0.5).to(dtype)
+    k = (torch.randn(pages, 16, hk, d, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(pages, 16, hk, d, generator=g) * 0.5).to(dtype)
+    scale = 1.0 / math.sqrt(d)
+    tree = PrefixTreeCPP(16)
+    tree.build_radix_tree(lens, _padded(tables))
+    tree.pack_schedule(None, hq // hk, hk)
+    tree.kernel_info.to_gpu(torch.device(DEV))
+    qd = qfull.to(DEV)[:, 1:]                           # [B, T, H, D] view with a larger batch stride
+    outfull = torch.full((B, T + 2, hq, d), float("nan"), dtype=dtype, device=DEV)
+    out = outfull[:, :T]
+    lse = torch.full((B, T, hq), float("nan"), device=DEV)
+    prefix_attn_with_kvcache(qd, k.to(DEV), v.to(DEV), tree, scale, out, lse_out=lse)
+    torch.cuda.synchronize()
+    P.check_status(DEV)
+    ref_o, ref_l = O.paged_multi_position_attention(qfull[:, 1:], k, v, lens, tables, scale)
+    _assert_close(out.float().cpu(), lse.cpu(), ref_o, ref_l, dtype)
+    assert torch.isnan(outfull[:, T:].float()).all()

@@ -231,3 +231,36 @@ def test_kernel_info_is_only_materialised_when_read(native_lib):
     assert info._vals is None                       # nothing has asked for the plan tensors yet
     assert info.max_split_per_seq >= 1 and len(info.q_tables) == len(info.MNWs) > 0
     assert info._vals is not None and info.num_split_per_seq.shape[0] == w.batch
+
+
+# ---------------------------------------------------------------------------------------------
+# Several query tokens per request
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T", [2, 3, 4, 8])
+@pytest.mark.parametrize("seed", [200, 201, 202, 203, 204, 205])
+def test_work_list_for_several_query_positions(seed, T, native_lib):
+    """Position t of a request sees its first len - T + 1 + t tokens; requests may be shorter than
+    a page, shorter than T + 1, and their last tokens may reach back into a shared segment."""
+    tr = _Trace(seed)
+    hratio, hk, page = (1, 2, 4, 8)[seed % 4], 2, tr.page
+    lens = [max(l, T) for l in tr.lens]                     # at least the T new tokens
+    tables = [t + tr._alloc(-(-l // page) - len(t)) if -(-l // page) > len(t) else t for t, l in zip(tr.tables, lens)]
+    tree = PrefixTreeCPP(page)
+    tree.build_radix_tree(lens, _padded(tables))
+    tree._hratio, tree._kv_heads = hratio, hk
+    cfg = P.WorkConfig(chunk_tokens_min=16, chunk_tokens_max=32) if seed % 2 else None
+    work = tree.kernel_info.device_work(CPU, cfg, T)
+    header, blob = _work_arrays(work)
+    assert header.q_per_req == T and header.batch == len(lens) * T and header.limits_off >= 0
+    g = torch.Generator().manual_seed(seed)
+    B, H, D = len(lens), hratio * hk, 32
+    q = (torch.randn(B, T, H, D, generator=g) * 0.5).bfloat16().float()
+    k = (torch.randn(tr.next_page, page, hk, D, generator=g) * 0.5).bfloat16().float()
+    v = (torch.randn(tr.next_page, page, hk, D, generator=g) * 0.5).bfloat16().float()
+    out, lse = W.execute(header, blob, q, k, v, 0.2)
+    ref_o, ref_l = O.paged_multi_position_attention(q, k, v, lens, tables, 0.2)
+    assert torch.allclose(out, ref_o, atol=2e-6, rtol=1e-5)
+    assert torch.allclose(lse, ref_l, atol=2e-6, rtol=1e-6)
+    # such a list is rebuilt, not advanced
+    tree.kernel_info._work = {k_: v_ for k_, v_ in tree.kernel_info._work.items()}
+    assert not tree.advance([l + 1 for l in lens], _padded(tables, max(len(t) for t in tables) + 2))

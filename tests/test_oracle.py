@@ -78,3 +78,26 @@ def test_merge_is_order_independent_and_exact():
     assert torch.allclose(a, b, atol=1e-6) and torch.allclose(la, lb, atol=1e-6)
     one, lone = O.merge_partials(o[:1], l[:1])
     assert torch.equal(one, o[0]) and torch.allclose(lone, l[0])
+
+
+GOLD_POS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_ref_positions.npz")
+
+
+@pytest.mark.parametrize("seed", [10, 11, 12])
+def test_multi_position_attention_matches_frozen_reference_outputs(seed):
+    """Several query tokens per request: frozen outputs of one real ``attention_ref`` call per
+    position (tests/golden/make_golden.py)."""
+    gold = np.load(GOLD_POS)
+    _, b, t_, h, hk, d, s = (int(x) for x in gold[f"spec{seed}"])
+    gen = torch.Generator().manual_seed(seed)
+    q = (torch.randn(b, t_, h, d, generator=gen) * 0.5).bfloat16().float()
+    k = (torch.randn(b, s, hk, d, generator=gen) * 0.5).bfloat16().float()
+    v = (torch.randn(b, s, hk, d, generator=gen) * 0.5).bfloat16().float()
+    lens = torch.randint(t_, s + 1, (b,), generator=gen)
+    assert lens.tolist() == gold[f"lens{seed}"].tolist()
+    out, lse = O.multi_position_attention(q, k, v, lens.tolist())
+    assert torch.allclose(out, torch.from_numpy(gold[f"out{seed}"]), atol=1e-6, rtol=1e-5)
+    # the last position is plain decode attention over the whole context
+    mask = torch.arange(s)[None, :] < lens[:, None]
+    last, last_lse = O.dense_attention(q[:, -1:], k, v, mask)
+    assert torch.equal(out[:, -1:], last) and torch.equal(lse[:, -1], last_lse[:, :, 0])

@@ -51,42 +51,55 @@ def items_of(header, blob):
 
 def execute(header, blob, q, k_cache, v_cache, scale):
     """Returns (out [B,H,D] fp32, lse [B,H] fp32)."""
-    B, _, H, D = q.shape
+    B, T, H, D = q.shape
     page, hk, hr = header.page_size, header.kv_heads, header.hratio
-    assert H == hk * hr
+    assert H == hk * hr and T == max(1, header.q_per_req) and header.batch == B * T
+    qv = q.reshape(B * T, 1, H, D)              # a query of the list is a (request, position) pair
     part_o = torch.zeros(header.num_entries, hr, D)
     part_l = torch.full((header.num_entries, hr), float("nan"))
     written = np.zeros(header.num_entries, dtype=np.int32)
     for idx, it in enumerate(items_of(header, blob)):
         q_off, nq, page_off, kv_len, entry_base, kv_head = (int(x) for x in it[:6])
+        tok_lo = int(it[7])
         streaming = idx < header.num_stream_items
         assert (kv_head == -1) == streaming
         qs = blob[header.queries_off + q_off: header.queries_off + q_off + nq].tolist()
+        if header.limits_off >= 0:      # tokens of the item each query may see
+            lim = blob[header.limits_off + q_off: header.limits_off + q_off + nq].tolist()
+            sees = [max(0, min(kv_len, l - tok_lo)) for l in lim]
+        else:
+            sees = [kv_len] * nq
         n_pages = -(-kv_len // page)
         pages = blob[header.pages_off + page_off: header.pages_off + page_off + n_pages].tolist()
         kk = O.gather_request_kv(k_cache, pages, kv_len)
         vv = O.gather_request_kv(v_cache, pages, kv_len)
         for kvh in (range(hk) if streaming else [kv_head]):
             heads = slice(kvh * hr, (kvh + 1) * hr)
-            o, l = O.segment_attention(q[qs, 0][:, heads], kk[:, kvh:kvh + 1], vv[:, kvh:kvh + 1], scale)
             for i in range(nq):
                 e = entry_base + (i * hk + kvh if streaming else i)
-                part_o[e], part_l[e] = o[i], l[i]
+                if sees[i] > 0:
+                    o, l = O.segment_attention(qv[qs[i]:qs[i] + 1, 0][:, heads], kk[:sees[i], kvh:kvh + 1],
+                                               vv[:sees[i], kvh:kvh + 1], scale)
+                    part_o[e], part_l[e] = o[0], l[0]
+                else:                   # sees nothing of this item: weight zero in the merge
+                    part_o[e], part_l[e] = 0.0, float("-inf")
                 written[e] += 1
     assert (written == 1).all(), "every entry must be written exactly once"
-    n_lists = B * hk
+    n_lists = B * T * hk
     indptr = blob[header.merge_indptr_off: header.merge_indptr_off + n_lists + 1]
     entries = blob[header.merge_entries_off: header.merge_entries_off + int(indptr[-1])]
     assert sorted(entries.tolist()) == list(range(header.num_entries)), "every entry is merged exactly once"
-    out = torch.zeros(B, H, D)
-    lse = torch.full((B, H), float("-inf"))
-    for b in range(B):
+    out = torch.zeros(B * T, H, D)
+    lse = torch.full((B * T, H), float("-inf"))
+    for b in range(B * T):
         for kvh in range(hk):
             lst = b * hk + kvh
             e = torch.as_tensor(entries[indptr[lst]: indptr[lst + 1]], dtype=torch.long)
             if len(e):
                 heads = slice(kvh * hr, (kvh + 1) * hr)
                 out[b, heads], lse[b, heads] = O.merge_partials(part_o[e], part_l[e])
+    if T > 1:
+        return out.reshape(B, T, H, D), lse.reshape(B, T, H)
     return out, lse
 
 
