@@ -8,9 +8,16 @@ they are remembered and attached to the ``num_split_per_seq`` tensor object;
 the op then finds them without reading anything back from the GPU.  A plan
 that arrives as bare tensors from elsewhere is copied back once (one
 synchronising D2H per new plan) and the result is cached on the same tensor.
+
+The cached host plan is matched by the identity and the version counter of the
+plan tensors.  A plan must therefore be REPLACED, not rewritten: tensors that
+are refilled through a raw pointer or a custom op (persistent metadata buffers
+of a captured graph) keep both, and the old work list would be used.  Callers
+that reuse buffers call ``invalidate(num_split_per_seq)`` after refilling them.
 """
 from __future__ import annotations
 
+import weakref
 from typing import List, Optional
 
 import numpy as np
@@ -75,14 +82,16 @@ class PlanTag:
 
     def __init__(self, host_plan: HostPlan, tensors):
         self.host_plan = host_plan
-        self.ids = tuple(id(t) for t in tensors)
         self.versions = tuple(t._version for t in tensors)
-        self.tensors = tensors          # keeps ids valid
+        # Weak references: the tag hangs on one of these tensors, so strong ones would form a
+        # cycle that keeps the device tensors and work lists alive until the cycle collector
+        # runs.  A dead reference (its id may have been reused) never matches.
+        self.refs = tuple(weakref.ref(t) for t in tensors)
         self.work = {}                  # (device, hratio, kv_heads, page, options) -> DeviceWork
 
     def matches(self, tensors) -> bool:
-        return (len(tensors) == len(self.ids)
-                and all(id(t) == i for t, i in zip(tensors, self.ids))
+        return (len(tensors) == len(self.refs)
+                and all(r() is t for t, r in zip(tensors, self.refs))
                 and all(t._version == v for t, v in zip(tensors, self.versions)))
 
 
@@ -111,3 +120,11 @@ def make_tag(num_split_per_seq, q_tables, block_tables, num_seqs, kv_lens) -> Pl
     tag = PlanTag(plan, plan_tensors(num_split_per_seq, q_tables, block_tables, num_seqs, kv_lens))
     num_split_per_seq._pat_plan_tag = tag
     return tag
+
+
+
+def invalidate(num_split_per_seq) -> None:
+    """Forgets the host plan and work lists cached on a plan's ``num_split_per_seq`` tensor (for
+    callers that refill their plan tensors in place)."""
+    if hasattr(num_split_per_seq, "_pat_plan_tag"):
+        del num_split_per_seq._pat_plan_tag

@@ -296,6 +296,21 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const int n_sub = (kv_len + 15) >> 4;
             const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
             const int32_t* item_pages = p.pages + page_off;
+            // The producers run up to R tiles ahead of the softmax warps.  The lanes of the K warp
+            // that issue no TMA use that lead to pull the Q rows of the NEXT item (scattered by
+            // query id) into L2, and with them the item record and the query ids into L1: the
+            // softmax warps, which fetch those rows between two tiles, then find them close by.
+            if (is_k && lane >= 8 && item + 1 < item_hi) {
+                const int32_t* nx = p.items + static_cast<size_t>(item + 1) * 8;
+                const int nq_off = __ldg(nx + 0), n_rows = __ldg(nx + 1) * p.hratio, n_kvh = __ldg(nx + 5);
+                for (int row = lane - 8; row < n_rows; row += 24) {
+                    const int qi = row / p.hratio, gg = row - qi * p.hratio;
+                    const T* q = q_row_ptr<T>(p, __ldg(p.queries + nq_off + qi), n_kvh * p.hratio + gg);
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
+                    if constexpr (D * sizeof(T) > 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q + 64));
+                }
+            }
+            __syncwarp();
             for (int j = 0; j < n_tiles; ++j, ++t) {
                 if (t >= R) ok = mbar_wait(empty + 8 * s, ph, p.wait_ns);
                 if (!ok) break;
@@ -398,7 +413,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             const bool qk = have_a && !a_new_item;
             const int sa = slot_add(s, 2);
             const uint32_t pha = sa < s ? ph ^ 1 : ph;
-            if (qk && ok) ok = mbar_wait(bar_full_k + 8 * sa, pha, p.wait_ns);
+            // O += P(g) V(g) first: at the end of an item the softmax warps wait for exactly this
+            // product, while S(g + 2) has two tiles of slack.
             if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph, p.wait_ns);
             if (ok) ok = mbar_wait(bar_p + 8 * s, ph, p.wait_ns);  // P(g) is in TMEM (over S(g))
             if (pv_j == 0 && pv_items > 0 && ok)
@@ -406,34 +422,43 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             ok = __all_sync(kFullMask, ok);     // keep the warp converged on a timeout
             if (!ok) break;                     // gave up: nothing more is issued
             tc_fence_after();
-            // slot sa held tile g - 1, whose P V was issued in the previous iteration; MMAs execute in
-            // issue order, so S(g + 2) may overwrite it now
             {
-                uint32_t q_w = q_lo, k_w = k_lo0 + sa * kSlotStep, v_w = v_lo0 + s * kSlotStep;
+                uint32_t v_w = v_lo0 + s * kSlotStep;
                 uint32_t p_col = tmem_base + s * kTcTile;
-                const uint32_t s_col = tmem_base + sa * kTcTile, o_col = tmem_base + tmem_o_col;
-                uint32_t acc_s = 0, acc_o = pv_j > 0 ? 1u : 0u;
+                const uint32_t o_col = tmem_base + tmem_o_col;
+                uint32_t acc_o = pv_j > 0 ? 1u : 0u;
 #pragma unroll
                 for (int i = 0; i < kTcTile / 16; ++i) {
-                    if (qk && i < kSteps && elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
                     if (elect_one()) tc_mma_ts(o_col, p_col, desc(v_w), idesc_pv, acc_o);
+                    v_w += 2048 >> 4;       // the next 16 tokens of V
+                    p_col += 8;             // 16 tokens of P = 8 packed columns
+                    acc_o = 1;
+                }
+            }
+            if (elect_one()) tc_commit(bar_o + 8 * s);
+            if (elect_one()) tc_commit(bar_empty_v + 8 * s);
+            // slot sa held tile g - 1, whose P V was issued in the previous iteration; MMAs execute in
+            // issue order, so S(g + 2) may overwrite it now
+            if (qk) {
+                ok = mbar_wait(bar_full_k + 8 * sa, pha, p.wait_ns);
+                ok = __all_sync(kFullMask, ok);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t q_w = q_lo, k_w = k_lo0 + sa * kSlotStep, acc_s = 0;
+                const uint32_t s_col = tmem_base + sa * kTcTile;
+#pragma unroll
+                for (int i = 0; i < kSteps; ++i) {
+                    if (elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
                     // k-step i + 1 of a K-major operand of 128 rows: 32 B on, or into the next 64-element box
                     const uint32_t step = (i & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
                     q_w += step;
                     k_w += step;
-                    v_w += 2048 >> 4;       // the next 16 tokens of V
-                    p_col += 8;             // 16 tokens of P = 8 packed columns
                     acc_s = 1;
-                    acc_o = 1;
                 }
-            }
-            if (qk) {
                 if (elect_one()) tc_commit(bar_s + 8 * sa);
                 if (elect_one()) tc_commit(bar_empty_k + 8 * sa);
                 qk_advance();
             }
-            if (elect_one()) tc_commit(bar_o + 8 * s);
-            if (elect_one()) tc_commit(bar_empty_v + 8 * s);
             if (++pv_j == pv_n) { ++pv_item; ++pv_items; pv_j = 0; pv_n = tiles_of(pv_item); }
             if (a_new_item) qk_alone(sa, pha);  // waits for the next item's Q, which the softmax warps
                                                 // write once they have seen the last S of this item

@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
     // wait for the dense kernel.  The partial results are only read after it, with ordinary loads.
     int b = 0, h = 0, g = 0, n = 0;
     const int32_t* ent = p.entries;
-    size_t my_slot = 0;
+    unsigned my_slot = 0;       // row of the partial buffers: entry * hratio + head in group (< 2^31 rows)
     if (have_row) {
         b = row / p.num_q_heads;
         h = row - b * p.num_q_heads;
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
         const int lo = __ldg(p.indptr + list);
         n = __ldg(p.indptr + list + 1) - lo;
         ent = p.entries + lo;
-        if (lane < n) my_slot = static_cast<size_t>(__ldg(ent + lane)) * p.hratio + g;
+        if (lane < n) my_slot = static_cast<unsigned>(__ldg(ent + lane)) * p.hratio + g;
     }
     if (p.sync) {
         if (threadIdx.x == 0) {
@@ -334,63 +334,64 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
         }
         __syncthreads();
     }
-    if (have_row) {
-    // Lane i owns entry i (and i + 32, ...): its slot and LSE are loaded side by side, then the
-    // partial rows are read four at a time (independent loads), the slot and weight of each
-    // coming from the owning lane by shuffle.  A list rarely has more than 32 entries.
-    float my_lse = -INFINITY;
-    if (lane < n) my_lse = p.part_lse[my_slot];
-    float gmax = my_lse;
-    for (int i = lane + 32; i < n; i += 32)
-        gmax = fmaxf(gmax, p.part_lse[static_cast<size_t>(__ldg(ent + i)) * p.hratio + g]);
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(kFullMask, gmax, d));
-
     float acc[kPer];
 #pragma unroll
     for (int k = 0; k < kPer; ++k) acc[k] = 0.f;
-    float wsum = 0.f;
-    for (int base = 0; base < n; base += 32) {
-        if (base > 0) {
-            my_slot = 0;
-            my_lse = -INFINITY;
-            if (base + lane < n) {
-                my_slot = static_cast<size_t>(__ldg(ent + base + lane)) * p.hratio + g;
-                my_lse = p.part_lse[my_slot];
+    float wsum = 0.f, gmax = -INFINITY;
+    if (have_row) {
+        // Lane i owns entry i (and i + 32, ...).  The partial rows are read four at a time, the row
+        // index and the weight of each coming from the owning lane by shuffle.  The addresses of
+        // the rows do not depend on the weights, so the first four rows are requested together
+        // with the LSEs: one dependent round trip to memory less per list.
+        auto load_row = [&](unsigned slot) {
+            const float* src = p.part_o + static_cast<size_t>(slot) * D + lane * kPer;
+            if constexpr (kPer == 4) {
+                return *reinterpret_cast<const float4*>(src);
+            } else {
+                const float2 y = *reinterpret_cast<const float2*>(src);
+                return make_float4(y.x, y.y, 0.f, 0.f);
             }
-        }
-        const float my_w = (my_lse == -INFINITY) ? 0.f : __expf(my_lse - gmax);    // 0 for lanes past the list
-        const int cnt = min(32, n - base);
-        const unsigned slot_lo = static_cast<unsigned>(my_slot), slot_hi = static_cast<unsigned>(my_slot >> 32);
-        for (int i = 0; i < cnt; i += 4) {
-            float w[4];
-            float4 x[4];
+        };
+        float4 x[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                // lanes past the list hold slot 0 and weight 0: a valid address, no contribution
-                const int src_lane = min(i + k, 31);
-                const size_t slot = (static_cast<size_t>(__shfl_sync(kFullMask, slot_hi, src_lane)) << 32) |
-                                    __shfl_sync(kFullMask, slot_lo, src_lane);
-                w[k] = (i + k < cnt) ? __shfl_sync(kFullMask, my_w, src_lane) : 0.f;
-                const float* src = p.part_o + slot * D + lane * kPer;
-                if constexpr (kPer == 4) {
-                    x[k] = *reinterpret_cast<const float4*>(src);
-                } else {
-                    const float2 y = *reinterpret_cast<const float2*>(src);
-                    x[k] = make_float4(y.x, y.y, 0.f, 0.f);
+        for (int k = 0; k < 4; ++k) x[k] = load_row(__shfl_sync(kFullMask, my_slot, k));   // lanes past the list: row 0, weight 0
+        float my_lse = lane < n ? p.part_lse[my_slot] : -INFINITY;
+        gmax = my_lse;
+        for (int i = lane + 32; i < n; i += 32)
+            gmax = fmaxf(gmax, p.part_lse[static_cast<size_t>(__ldg(ent + i)) * p.hratio + g]);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(kFullMask, gmax, d));
+
+        for (int base = 0; base < n; base += 32) {
+            if (base > 0) {
+                my_slot = 0;
+                my_lse = -INFINITY;
+                if (base + lane < n) {
+                    my_slot = static_cast<unsigned>(__ldg(ent + base + lane)) * p.hratio + g;
+                    my_lse = p.part_lse[my_slot];
                 }
             }
+            const float my_w = (my_lse == -INFINITY) ? 0.f : __expf(my_lse - gmax);    // 0 for lanes past the list
+            const int cnt = min(32, n - base);
+            for (int i = 0; i < cnt; i += 4) {
+                float w[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                if (w[k] != 0.f) {      // a skipped row may hold anything (never written slots are not read: w = 0)
-                    wsum += w[k];
-                    acc[0] += w[k] * x[k].x;
-                    acc[1] += w[k] * x[k].y;
-                    if constexpr (kPer == 4) { acc[2] += w[k] * x[k].z; acc[3] += w[k] * x[k].w; }
+                for (int k = 0; k < 4; ++k) {
+                    const int src_lane = min(i + k, 31);
+                    if (base > 0 || i > 0) x[k] = load_row(__shfl_sync(kFullMask, my_slot, src_lane));
+                    w[k] = (i + k < cnt) ? __shfl_sync(kFullMask, my_w, src_lane) : 0.f;
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (w[k] != 0.f) {      // a skipped row may hold anything (never written slots are not read: w = 0)
+                        wsum += w[k];
+                        acc[0] += w[k] * x[k].x;
+                        acc[1] += w[k] * x[k].y;
+                        if constexpr (kPer == 4) { acc[2] += w[k] * x[k].z; acc[3] += w[k] * x[k].w; }
+                    }
                 }
             }
         }
-    }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
     const int req = p.q_per_req == 1 ? b : b / p.q_per_req;
     T* dst = static_cast<T*>(p.out) + static_cast<int64_t>(req) * p.out_batch_stride +
