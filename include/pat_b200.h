@@ -148,6 +148,8 @@ typedef struct pat_work_header {
     int64_t dense_unique_tokens;
     int32_t q_per_req;              /* query tokens per request the list was built for (1 = decode) */
     int32_t limits_off;             /* per-(segment, query) visible-token limits, or -1 */
+    int32_t dense_q_off;            /* query ids of the dense items, dense_q_width per item, -1 padded */
+    int32_t dense_q_width;
 } pat_work_header;
 
 /* Returns NULL and sets *status on failure. num_cache_pages > 0 enables a range check of page ids. */

@@ -10,6 +10,10 @@ from .data_class import PackedBox, Sequence, SeqGroup, KernelInfo
 from .block_scheduler import pack_prefix_blocks, pack_without_prefix, schedule, schedule_naive
 from .prefix_tree import PrefixTree
 from .async_tree import AsyncTree
+# not part of the reference's export list: carrying a plan across decode steps, and the report of
+# a kernel whose bounded wait ran out
+from ._prefix_attn import check_status, status_word
+from .planner import DecodePlanner
 
 __all__ = [
     "prefix_attn_with_kvcache",

@@ -45,7 +45,8 @@ class WorkHeader(C.Structure):
                 ("blob_words", C.c_int32), ("num_segments", C.c_int32), ("max_page_id", C.c_int32),
                 ("unique_tokens", C.c_int64), ("stream_tokens", C.c_int64), ("dense_tokens", C.c_int64),
                 ("stream_unique_tokens", C.c_int64), ("dense_unique_tokens", C.c_int64),
-                ("q_per_req", C.c_int32), ("limits_off", C.c_int32)]
+                ("q_per_req", C.c_int32), ("limits_off", C.c_int32),
+                ("dense_q_off", C.c_int32), ("dense_q_width", C.c_int32)]
 
 
 class DecodeArgs(C.Structure):

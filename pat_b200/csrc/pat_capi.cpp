@@ -56,13 +56,15 @@ void copy_header(const pat::WorkHeader& h, pat_work_header* out) {
     out->dense_unique_tokens = h.dense_unique_tokens;
     out->q_per_req = h.q_per_req;
     out->limits_off = h.limits_off;
+    out->dense_q_off = h.dense_q_off;
+    out->dense_q_width = h.dense_q_width;
 }
 
 }  // namespace
 
 extern "C" {
 
-int pat_b200_abi_version(void) { return 3; }
+int pat_b200_abi_version(void) { return 4; }
 
 const char* pat_b200_strerror(int status) {
     switch (status) {

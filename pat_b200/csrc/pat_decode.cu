@@ -156,6 +156,8 @@ int launch_all(const pat_decode_args& a, cudaStream_t stream, int dev) {
         DenseTcParams dp{};
         dp.a = pd;
         dp.cta_begin = a.work_blob + a.work.dense_cta_off;
+        dp.dense_q = a.work_blob + a.work.dense_q_off;
+        dp.dense_q_width = a.work.dense_q_width;
         dp.sync = sync;
         kern<<<static_cast<unsigned>(a.work.num_dense_ctas), kTcThreads, smem, stream>>>(dp, kmap, vmap);
         ++launches;

@@ -200,6 +200,8 @@ template <int N> __device__ __forceinline__ void tmem_st_f(uint32_t taddr, const
 struct DenseTcParams {
     AttnParams a;
     const int32_t* cta_begin;   // [num_ctas + 1] first dense item of each CTA
+    const int32_t* dense_q;     // [num_items][dense_q_width] query ids of every item, -1 past its queries
+    int dense_q_width;
     // Control words at the head of the workspace, or null.  Set when the streaming kernel runs
     // beside this one: the merge kernel is then ordered after the streaming kernel only, so every
     // CTA of this kernel counts itself out when its partial results are written and the last one
@@ -361,7 +363,6 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         const uint32_t k_lo0 = ((sK >> 4) & 0x3fffu) | (1u << 16);
         const uint32_t v_lo0 = ((sV >> 4) & 0x3fffu) | (static_cast<uint32_t>((kTcTile * 128) >> 4) << 16);   // MN-major: next 64 elements
         auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kHi) << 32) | lo; };
-        auto slot_add = [](int s, int d) { const int x = s + d; return x >= R ? x - R : x; };
 
         // The CTA's items form one stream of tiles g = 0, 1, ...: S(g + 2) is requested while tile g
         // is multiplied into O, across item boundaries too, so that a new item costs no pipeline
@@ -374,48 +375,50 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         int total_tiles = 0;
         for (int item = item_lo; item < item_hi; ++item) total_tiles += tiles_of(item);
         int qk_item = item_lo, qk_j = 0, qk_n = tiles_of(item_lo), qk_items = 0;     // cursor of the next Q K^T
+        int qk_tile = 0;                                                             // its index in the tile stream
         int pv_j = 0, pv_n = qk_n, pv_item = item_lo, pv_items = 0;                  // cursor of the next P V
-        auto qk_advance = [&]() {
-            if (++qk_j == qk_n) { ++qk_item; qk_j = 0; qk_n = tiles_of(qk_item); }
-        };
-        // S(tile at the cursor) = Q K^T into ring slot `slot`; on its own (not interleaved)
-        auto qk_alone = [&](int slot, uint32_t phase) {
-            if (qk_j == 0) {            // a new item: its Q rows must be in shared memory
-                if (ok) ok = mbar_wait(bar_q, qk_items & 1, p.wait_ns);
-                ++qk_items;
-            }
-            if (ok) ok = mbar_wait(bar_full_k + 8 * slot, phase, p.wait_ns);
-            ok = __all_sync(kFullMask, ok);
-            if (!ok) return;            // gave up: nothing more is issued
-            tc_fence_after();
-            {
+        // S products are issued strictly in tile order, up to two tiles ahead of the P V products
+        // (ring slot of tile g + 2 = slot of tile g - 1, whose P V was issued an iteration ago; MMAs
+        // execute in issue order).  The first S of an item needs the item's Q rows, which the
+        // softmax warps write once they have handed the previous item's last P over - so it is
+        // issued only after that item's last P V: nothing the epilogue waits for queues behind it.
+        auto issue_qk_upto = [&](int pv_done) {     // pv_done: last tile whose P V has been issued (-1: none)
+            while (ok && qk_tile < total_tiles && qk_tile <= pv_done + 2) {
+                const bool opens = qk_j == 0;
+                if (opens && qk_tile > pv_done + 1) break;
+                const int slot = qk_tile % R;
+                const uint32_t phase = static_cast<uint32_t>(qk_tile / R) & 1u;
+                if (opens) {
+                    ok = mbar_wait(bar_q, qk_items & 1, p.wait_ns);
+                    ++qk_items;
+                    fence_async_smem();     // the Q rows were written through the generic proxy
+                }
+                if (ok) ok = mbar_wait(bar_full_k + 8 * slot, phase, p.wait_ns);
+                ok = __all_sync(kFullMask, ok);
+                if (!ok) return;            // gave up: nothing more is issued
+                tc_fence_after();
                 uint32_t q_w = q_lo, k_w = k_lo0 + slot * kSlotStep, acc = 0;
 #pragma unroll
                 for (int ks = 0; ks < kSteps; ++ks) {
                     if (elect_one()) tc_mma(tmem_base + slot * kTcTile, desc(q_w), desc(k_w), idesc_qk, acc);
+                    // k-step ks + 1 of a K-major operand of 128 rows: 32 B on, or into the next 64-element box
                     const uint32_t step = (ks & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
                     q_w += step;
                     k_w += step;
                     acc = 1;
                 }
+                if (elect_one()) tc_commit(bar_s + 8 * slot);
+                if (elect_one()) tc_commit(bar_empty_k + 8 * slot);    // the K tile is free once this product has completed
+                if (++qk_j == qk_n) { ++qk_item; qk_j = 0; qk_n = tiles_of(qk_item); }
+                ++qk_tile;
             }
-            if (elect_one()) tc_commit(bar_s + 8 * slot);
-            if (elect_one()) tc_commit(bar_empty_k + 8 * slot);    // the K tile is free once this product has completed
-            qk_advance();
         };
         int s = 0;                              // ring slot and phase of tile g
         uint32_t ph = 0;
-        qk_alone(0, 0);
-        if (ok && total_tiles > 1) qk_alone(1, 0);
+        issue_qk_upto(-1);
         for (int g = 0; g < total_tiles && ok; ++g) {
-            const bool have_a = g + 2 < total_tiles;
-            const bool a_new_item = have_a && qk_j == 0;       // S(g + 2) opens an item: issued after P V(g)
-            const bool qk = have_a && !a_new_item;
-            const int sa = slot_add(s, 2);
-            const uint32_t pha = sa < s ? ph ^ 1 : ph;
-            // O += P(g) V(g) first: at the end of an item the softmax warps wait for exactly this
-            // product, while S(g + 2) has two tiles of slack.
-            if (ok) ok = mbar_wait(bar_full_v + 8 * s, ph, p.wait_ns);
+            // O += P(g) V(g)
+            ok = mbar_wait(bar_full_v + 8 * s, ph, p.wait_ns);
             if (ok) ok = mbar_wait(bar_p + 8 * s, ph, p.wait_ns);  // P(g) is in TMEM (over S(g))
             if (pv_j == 0 && pv_items > 0 && ok)
                 ok = mbar_wait(bar_ofree, (pv_items - 1) & 1, p.wait_ns);   // the softmax warps have read the previous item's O
@@ -437,31 +440,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             }
             if (elect_one()) tc_commit(bar_o + 8 * s);
             if (elect_one()) tc_commit(bar_empty_v + 8 * s);
-            // slot sa held tile g - 1, whose P V was issued in the previous iteration; MMAs execute in
-            // issue order, so S(g + 2) may overwrite it now
-            if (qk) {
-                ok = mbar_wait(bar_full_k + 8 * sa, pha, p.wait_ns);
-                ok = __all_sync(kFullMask, ok);
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t q_w = q_lo, k_w = k_lo0 + sa * kSlotStep, acc_s = 0;
-                const uint32_t s_col = tmem_base + sa * kTcTile;
-#pragma unroll
-                for (int i = 0; i < kSteps; ++i) {
-                    if (elect_one()) tc_mma(s_col, desc(q_w), desc(k_w), idesc_qk, acc_s);
-                    // k-step i + 1 of a K-major operand of 128 rows: 32 B on, or into the next 64-element box
-                    const uint32_t step = (i & 3) == 3 ? ((128 * 128 - 96) >> 4) : (32 >> 4);
-                    q_w += step;
-                    k_w += step;
-                    acc_s = 1;
-                }
-                if (elect_one()) tc_commit(bar_s + 8 * sa);
-                if (elect_one()) tc_commit(bar_empty_k + 8 * sa);
-                qk_advance();
-            }
             if (++pv_j == pv_n) { ++pv_item; ++pv_items; pv_j = 0; pv_n = tiles_of(pv_item); }
-            if (a_new_item) qk_alone(sa, pha);  // waits for the next item's Q, which the softmax warps
-                                                // write once they have seen the last S of this item
+            issue_qk_upto(g);
             if (++s == R) { s = 0; ph ^= 1; }
         }
         if (!ok) {
@@ -498,16 +478,16 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         tc_fence_after();
     };
     auto pair_sync = [&]() { named_bar_sync(2 + quad, 64); };   // the two warps that share TMEM lanes
-    // Q rows of an item, half a row per thread: global -> registers, registers -> the swizzled
-    // K-major layout in shared memory (the address takes two dependent loads, so it is worked
-    // out an item ahead)
-    auto q_addr = [&](int item) -> const uint4* {
-        const int32_t* it = p.items + static_cast<size_t>(item) * 8;
-        const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kvh = __ldg(it + 5);
-        if (r >= nq * p.hratio) return nullptr;
-        const int qi = r / p.hratio, gg = r - qi * p.hratio;
-        const T* q = q_row_ptr<T>(p, __ldg(p.queries + q_off + qi), kvh * p.hratio + gg);
-        return reinterpret_cast<const uint4*>(q) + half * (D / 16);
+    // Q rows of an item, half a row per thread.  A load from global memory takes a thousand
+    // clocks or more here (the producers keep the memory system busy), so nothing on the way to a
+    // row's address waits for anything else: the query id of this thread's row comes from a table
+    // indexed by the item number alone, and item records (two 16-byte words) are loaded an item
+    // ahead; both are requested at the top of the item before.
+    const int my_q = r / p.hratio, my_g = r - my_q * p.hratio;
+    auto q_id = [&](int item) { return my_q < dp.dense_q_width ? __ldg(dp.dense_q + static_cast<size_t>(item) * dp.dense_q_width + my_q) : -1; };
+    auto q_addr = [&](int qid, int kvh) -> const uint4* {
+        if (qid < 0) return nullptr;
+        return reinterpret_cast<const uint4*>(q_row_ptr<T>(p, qid, kvh * p.hratio + my_g)) + half * (D / 16);
     };
     auto q_fetch = [&](const uint4* src, uint4 (&qv)[D / 16]) {
 #pragma unroll
@@ -522,43 +502,64 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
         }
         fence_async_smem();
     };
+    // record of an item: {q_off, nq, page_off, kv_len}, {entry_base, kv_head, cost, tok_lo}
+    auto load_record = [&](int item, int4& a, int4& b) {
+        const int4* rec = reinterpret_cast<const int4*>(p.items + static_cast<size_t>(item) * 8);
+        a = __ldg(rec);
+        b = __ldg(rec + 1);
+    };
+    int4 rec_a, rec_b;
+    load_record(item_lo, rec_a, rec_b);
     for (int item = item_lo; item < item_hi; ++item) {
-        const int32_t* it = p.items + static_cast<size_t>(item) * 8;
-        const int q_off = __ldg(it + 0), nq = __ldg(it + 1), kv_len = __ldg(it + 3), entry_base = __ldg(it + 4),
-                  kvh = __ldg(it + 5);
+        const int q_off = rec_a.x, nq = rec_a.y, kv_len = rec_a.w, entry_base = rec_b.x;
         const int rows_valid = nq * p.hratio;
         const int n_tiles = (kv_len + kTcTile - 1) / kTcTile;
         int row_limit = kv_len;             // tokens of this item that row r may see
         if constexpr (kLimits)
-            row_limit = r < rows_valid ? visible_tokens(p, q_off + r / p.hratio, __ldg(it + 7), kv_len) : 0;
+            row_limit = r < rows_valid ? visible_tokens(p, q_off + r / p.hratio, rec_b.w, kv_len) : 0;
+        int4 next_a = make_int4(0, 0, 0, 0), next_b = make_int4(0, 0, 0, 0);
+        int next_qid = -1;
+        if (item + 1 < item_hi) {           // in flight during this item's tiles
+            load_record(item + 1, next_a, next_b);
+            next_qid = q_id(item + 1);
+        }
 
         // the first item's Q rows; those of every later item are written during the last tile of the
         // item before it (below)
         if (item == item_lo) {
             uint4 qv[D / 16];
-            q_fetch(q_addr(item), qv);
+            q_fetch(q_addr(q_id(item), rec_b.y), qv);
             q_store(qv);
             tc_fence_before();
             mbar_arrive(bar_q);
         }
 
-        const uint4* q_next = item + 1 < item_hi ? q_addr(item + 1) : nullptr;
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < n_tiles; ++j, ++t) {
+            if (ok) ok = mbar_wait(bar_s + 8 * s, ph, p.wait_ns);
+            tc_fence_after();
             if (j == n_tiles - 1 && item + 1 < item_hi) {
-                // Last tile of the item.  Once its S has completed, so has every Q K^T of the item,
-                // and the Q rows of the next item can take their place: the MMA warp then requests
-                // that item's first S tiles while this item is still being finished.
-                uint4 qv[D / 16];
-                q_fetch(q_next, qv);            // in flight during the wait
-                if (ok) ok = mbar_wait(bar_s + 8 * s, ph, p.wait_ns);
-                tc_fence_after();
-                q_store(qv);
-                tc_fence_before();
-                mbar_arrive(bar_q);
-            } else {
-                if (ok) ok = mbar_wait(bar_s + 8 * s, ph, p.wait_ns);
-                tc_fence_after();
+                // Last tile of the item.  Its S has completed, and with it every Q K^T of the item:
+                // the Q rows of the next item can take their place.  They are copied from global
+                // memory (from L2: the K producer warp has prefetched them) straight into the swizzled
+                // layout by asynchronous 16-byte copies that take no registers and nobody waits for:
+                // each thread's copies arrive on q_ready by themselves when they have landed, which
+                // is during this tile's softmax, and the MMA warp - which issues a proxy fence after
+                // that wait - can request the next item's first S right after this item's last P V.
+                const uint4* src = q_addr(next_qid, next_b.y);
+#pragma unroll
+                for (int i = 0; i < D / 16; ++i) {
+                    const int ch = half * (D / 16) + i;
+                    const uint32_t dst = sQ + (ch >> 3) * (128 * 128) + swz128(r, ch & 7);
+                    if (src) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + i) : "memory");
+                    else asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+                }
+                if (src) {
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_q) : "memory");
+                } else {            // a row beyond the item's queries: zeros, written synchronously
+                    fence_async_smem();
+                    mbar_arrive(bar_q);
+                }
             }
             constexpr int CH = kTcTile / 2;     // token columns per thread
             float sc[CH];
@@ -672,6 +673,8 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
                     p.part_lse[slot] = (!kLimits || l_row > 0.f) ? m_used * p.scale + logf(l_row) : -INFINITY;
             }
         }
+        rec_a = next_a;
+        rec_b = next_b;
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     }

@@ -535,7 +535,9 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     const size_t items_off = 0;
     const size_t queries_off = align8(items_off + n_items * 8);
     const size_t limits_off = align8(queries_off + queries_sec.size());
-    const size_t pages_off = align8(limits_off + limits_sec.size());
+    const size_t dense_q_off = align8(limits_off + limits_sec.size());
+    const size_t dense_q_width = static_cast<size_t>(std::max(1, q_per_dense));
+    const size_t pages_off = align8(dense_q_off + dense_items.size() * dense_q_width);
     const size_t cta_off = align8(pages_off + pages_sec.size());
     const size_t indptr_off = align8(cta_off + cta_begin.size());
     const size_t entries_off = align8(indptr_off + indptr.size());
@@ -548,6 +550,12 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
                     dense_items.size() * sizeof(WorkItem));
     std::copy(queries_sec.begin(), queries_sec.end(), blob_.begin() + queries_off);
     std::copy(limits_sec.begin(), limits_sec.end(), blob_.begin() + limits_off);
+    for (size_t d = 0; d < dense_items.size(); ++d) {
+        int32_t* row = blob_.data() + dense_q_off + d * dense_q_width;
+        const WorkItem& it = dense_items[d];
+        for (size_t i = 0; i < dense_q_width; ++i)
+            row[i] = static_cast<int>(i) < it.nq ? queries_sec[it.q_off + i] : -1;
+    }
     std::copy(pages_sec.begin(), pages_sec.end(), blob_.begin() + pages_off);
     std::copy(cta_begin.begin(), cta_begin.end(), blob_.begin() + cta_off);
     std::copy(indptr.begin(), indptr.end(), blob_.begin() + indptr_off);
@@ -575,6 +583,8 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     header_.unique_tokens = unique_tokens;
     header_.q_per_req = 1;
     header_.limits_off = any_limits ? static_cast<int32_t>(limits_off) : -1;
+    header_.dense_q_off = static_cast<int32_t>(dense_q_off);
+    header_.dense_q_width = static_cast<int32_t>(dense_q_width);
     for (GrowSlot& g : grow_)
         if (g.item >= 0) g.next_page += static_cast<int32_t>(pages_off);
     return 0;

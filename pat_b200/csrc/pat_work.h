@@ -106,6 +106,11 @@ struct WorkHeader {
     // sees all tokens of its segments (q_per_req = 1).
     int32_t q_per_req;
     int32_t limits_off;
+    // Query ids of the dense items as a table with a fixed row width (dense_rows / hratio ids per
+    // item, -1 past an item's queries): the dense kernel fetches an item's ids without first
+    // having read the item's record.
+    int32_t dense_q_off;
+    int32_t dense_q_width;
 };
 
 // A set of pages attended by the same queries (host-side intermediate of the builders).

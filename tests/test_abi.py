@@ -27,15 +27,15 @@ def test_every_declared_symbol_is_exported_and_bound(native_lib):
 
 
 def test_structs_match_the_header_sizes(native_lib):
-    # pat_work_header: 18 int32 + 5 int64 + 2 int32; pat_work_options: 10 int32; pat_plan_bucket: 4 int32 + 4 ptr
-    assert C.sizeof(N.WorkHeader) == 18 * 4 + 5 * 8 + 2 * 4
+    # pat_work_header: 18 int32 + 5 int64 + 4 int32; pat_work_options: 10 int32; pat_plan_bucket: 4 int32 + 4 ptr
+    assert C.sizeof(N.WorkHeader) == 18 * 4 + 5 * 8 + 4 * 4
     assert C.sizeof(N.WorkOptions) == 40
     assert C.sizeof(N.PlanBucket) == 16 + 4 * 8
     assert C.sizeof(N.BucketView) == 24 + 5 * 8
 
 
 def test_version_and_strerror(native_lib):
-    assert native_lib.pat_b200_abi_version() >= 3
+    assert native_lib.pat_b200_abi_version() >= 4
     assert N.strerror(0) == "ok"
     assert "workspace" in N.strerror(-12)
     assert N.strerror(-999) == "unknown status"

@@ -148,6 +148,12 @@ def test_full_configs_dedup_every_page(cfg, native_lib):
     entries = blob[header.merge_entries_off: header.merge_entries_off + int(indptr[-1])]
     assert indptr[-1] == header.num_entries
     assert sorted(entries.tolist()) == list(range(header.num_entries))
+    # the dense kernel's query-id table repeats the dense items' query lists at a fixed row width
+    width = header.dense_q_width
+    table = blob[header.dense_q_off: header.dense_q_off + header.num_dense_items * width].reshape(-1, width)
+    for d, it in enumerate(items[header.num_stream_items:]):
+        want = blob[header.queries_off + it[0]: header.queries_off + it[0] + it[1]].tolist()
+        assert table[d, :it[1]].tolist() == want and (table[d, it[1]:] == -1).all()
     # streaming items: longest first
     costs = items[:header.num_stream_items, 6]
     assert (np.diff(costs) <= 0).all()
