@@ -303,11 +303,14 @@ dense_tc_kernel(const DenseTcParams dp, const __grid_constant__ CUtensorMap kmap
             // query id) into L2, and with them the item record and the query ids into L1: the
             // softmax warps, which fetch those rows between two tiles, then find them close by.
             if (is_k && lane >= 8 && item + 1 < item_hi) {
-                const int32_t* nx = p.items + static_cast<size_t>(item + 1) * 8;
-                const int nq_off = __ldg(nx + 0), n_rows = __ldg(nx + 1) * p.hratio, n_kvh = __ldg(nx + 5);
+                // (the same record words and id-table row the softmax warps will read: they end up in
+                // this SM's L1 as well)
+                const int4* nx = reinterpret_cast<const int4*>(p.items + static_cast<size_t>(item + 1) * 8);
+                const int n_rows = __ldg(nx).y * p.hratio, n_kvh = __ldg(nx + 1).y;
+                const int32_t* ids = dp.dense_q + static_cast<size_t>(item + 1) * dp.dense_q_width;
                 for (int row = lane - 8; row < n_rows; row += 24) {
                     const int qi = row / p.hratio, gg = row - qi * p.hratio;
-                    const T* q = q_row_ptr<T>(p, __ldg(p.queries + nq_off + qi), n_kvh * p.hratio + gg);
+                    const T* q = q_row_ptr<T>(p, __ldg(ids + qi), n_kvh * p.hratio + gg);
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
                     if constexpr (D * sizeof(T) > 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q + 64));
                 }

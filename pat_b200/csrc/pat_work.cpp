@@ -367,7 +367,7 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     }
     for (WorkItem& it : stream_items) it.kv_head = -1;
 
-    // ---- 6. dense items: equal token shares per persistent CTA ------------------
+    // ---- 6. dense items: equal work per persistent CTA ------------------------------
     // The token ranges of the dense segments are laid end to end and cut into `shares` parts of
     // equal cost.  A share is executed by kv_heads x row_lanes CTAs at the same time
     // (CTA id = (share * kv_heads + head) * row_lanes + lane): one per KV head and per 128-row
@@ -397,7 +397,7 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
         const int64_t min_piece = std::max<int64_t>(granule, opt.dense_piece_tokens_min);
         // cost unit: tokens x row chunks (what the row lanes of a share work off together); every
         // item costs about as much as kItemTokens more tokens (pipeline fill, epilogue)
-        constexpr int64_t kItemTokens = 256;
+        constexpr int64_t kItemTokens = 384;
         auto passes = [&](const DenseSeg& d) { return static_cast<int64_t>(d.chunks); };
         int64_t total_cost = 0;
         for (const DenseSeg& d : dsegs) total_cost += (d.sg->tokens + kItemTokens) * passes(d);
@@ -432,76 +432,101 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
             }
         }
         const int64_t shares = std::min<int64_t>(share_limit, std::max<int64_t>(1, total_cost / row_lanes / min_piece));
-        struct Piece { const DenseSeg* d; int64_t pos, take; };
-        // Walk the segments and fill one share after the other up to `target` cost units, cutting
-        // segments on granule boundaries where a share is full.  How many pieces that makes - and
-        // with it the per-item part of the cost - is only known afterwards, so the target starts
-        // at the even split and is raised a little until the shares at hand hold everything.
-        std::vector<std::vector<Piece>> share_pieces;
-        auto cut = [&](int64_t target) {
-            share_pieces.assign(1, {});
-            int64_t used = 0;
-            for (const DenseSeg& d : dsegs) {
-                const int64_t tokens = d.sg->tokens, w = passes(d);
-                int64_t pos = 0;
-                while (pos < tokens) {
-                    int64_t cap = (target - used) / w - kItemTokens;            // tokens of this segment that still fit
-                    cap = cap / granule * granule;
-                    if (cap < granule && used > 0) {                            // full: open the next share
-                        share_pieces.emplace_back();
-                        used = 0;
-                        continue;
+        // Jobs: one per (piece, 128-row chunk), placed on the CTAs (share x row lane; the same
+        // placement for every KV head).
+        //  * Long segments - thousands of tokens, one chunk a good part of a CTA's fair share - are
+        //    cut along their tokens: they are laid end to end and one
+        //    share after the other is filled up to the fair load, cutting on granule boundaries;
+        //    inside a share every chunk goes to the row lane with the least work so far, so the
+        //    chunks of one piece run side by side (a 2 KB cache row - all heads of a token - is then
+        //    fetched from HBM within a short window and the second row chunk finds it in L2).
+        //  * Short segments - the nodes of a deep tree - stay whole, since every cut costs another
+        //    item: their chunks go, longest first, to the CTA with the least work so far.
+        struct Job { const DenseSeg* d; int chunk; int64_t pos, take; };
+        const int64_t bins = shares * row_lanes;
+        const int64_t fair = (total_cost + bins - 1) / bins;
+        std::vector<std::vector<Job>> bin_jobs(static_cast<size_t>(bins));
+        std::vector<int64_t> load(static_cast<size_t>(bins), 0);
+        std::vector<DenseSeg> long_segs, short_segs;
+        for (const DenseSeg& d : dsegs) {
+            const bool is_long = d.sg->tokens + kItemTokens > fair / 4 && d.sg->tokens >= 4 * kItemTokens;
+            (is_long ? long_segs : short_segs).push_back(d);
+        }
+        if (!long_segs.empty()) {
+            struct Piece { const DenseSeg* d; int64_t pos, take; };
+            std::vector<std::vector<Piece>> share_pieces;
+            auto cut = [&](int64_t target) {
+                share_pieces.assign(1, {});
+                int64_t used = 0;
+                for (const DenseSeg& d : long_segs) {
+                    const int64_t tokens = d.sg->tokens, w = passes(d);
+                    int64_t pos = 0;
+                    while (pos < tokens) {
+                        int64_t cap = (target - used) / w - kItemTokens;            // tokens of this segment that still fit
+                        cap = cap / granule * granule;
+                        if (cap < granule && used > 0) {                            // full: open the next share
+                            share_pieces.emplace_back();
+                            used = 0;
+                            continue;
+                        }
+                        int64_t take = std::min(tokens - pos, std::max(cap, granule));
+                        // do not leave a sliver behind
+                        if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
+                        share_pieces.back().push_back(Piece{&d, pos, take});
+                        used += (take + kItemTokens) * w;
+                        pos += take;
                     }
-                    int64_t take = std::min(tokens - pos, std::max(cap, granule));
-                    // do not leave a sliver behind
-                    if (tokens - pos - take > 0 && tokens - pos - take < granule) take = tokens - pos;
-                    share_pieces.back().push_back(Piece{&d, pos, take});
-                    used += (take + kItemTokens) * w;
-                    pos += take;
+                }
+                return static_cast<int64_t>(share_pieces.size());
+            };
+            int64_t target = fair * row_lanes;
+            while (cut(target) > shares) target += std::max<int64_t>(target / 32, 1);
+            for (size_t sh = 0; sh < share_pieces.size(); ++sh) {
+                for (const Piece& pc : share_pieces[sh]) {
+                    for (int chunk = 0; chunk < pc.d->chunks; ++chunk) {
+                        size_t best = sh * row_lanes;
+                        for (size_t b = best + 1; b < (sh + 1) * row_lanes; ++b)
+                            if (load[b] < load[best]) best = b;
+                        bin_jobs[best].push_back(Job{pc.d, chunk, pc.pos, pc.take});
+                        load[best] += pc.take + kItemTokens;
+                    }
                 }
             }
-            return static_cast<int64_t>(share_pieces.size());
-        };
-        int64_t target = (total_cost + shares - 1) / shares;
-        while (cut(target) > shares) target += std::max<int64_t>(target / 32, 1);
-        struct LaneJob { const Piece* pc; int chunk; };
-        std::vector<std::vector<LaneJob>> lane_jobs(row_lanes);
-        for (const auto& pieces : share_pieces) {
-            std::vector<int64_t> load(row_lanes, 0);
-            for (auto& jobs : lane_jobs) jobs.clear();
-            for (const Piece& pc : pieces) {
-                for (int chunk = 0; chunk < pc.d->chunks; ++chunk) {
-                    int lane = 0;
-                    for (int l = 1; l < row_lanes; ++l)
-                        if (load[l] < load[lane]) lane = l;
-                    lane_jobs[lane].push_back(LaneJob{&pc, chunk});
-                    load[lane] += pc.take + kItemTokens;
-                }
+        }
+        {
+            std::vector<Job> jobs;
+            for (const DenseSeg& d : short_segs)
+                for (int chunk = 0; chunk < d.chunks; ++chunk) jobs.push_back(Job{&d, chunk, 0, d.sg->tokens});
+            std::stable_sort(jobs.begin(), jobs.end(), [](const Job& a, const Job& b) { return a.take > b.take; });
+            for (const Job& job : jobs) {
+                size_t best = 0;
+                for (size_t b = 1; b < load.size(); ++b)
+                    if (load[b] < load[best]) best = b;
+                bin_jobs[best].push_back(job);
+                load[best] += job.take + kItemTokens;
             }
+        }
+        for (int64_t share = 0; share < shares; ++share) {
             for (int h = 0; h < kv_heads; ++h) {
                 for (int lane = 0; lane < row_lanes; ++lane) {
                     cta_begin.push_back(static_cast<int32_t>(dense_items.size()));
-                    for (const LaneJob& job : lane_jobs[lane]) {
-                        const Piece& pc = *job.pc;
-                        const Segment* sg = pc.d->sg;
+                    for (const Job& job : bin_jobs[static_cast<size_t>(share * row_lanes + lane)]) {
+                        const Segment* sg = job.d->sg;
                         const int nq_all = static_cast<int>(sg->queries.size());
-                        {
-                            const int chunk = job.chunk;
-                            const int q0 = chunk * q_per_dense;
-                            WorkItem it{};
-                            it.q_off = sg->q_off + q0;
-                            it.nq = std::min(q_per_dense, nq_all - q0);
-                            it.page_off = sg->page_off + static_cast<int32_t>(pc.pos / page_size);
-                            it.kv_len = static_cast<int32_t>(pc.take);
-                            it.entry_base = num_entries;
-                            it.kv_head = h;
-                            it.cost = static_cast<int32_t>(pc.take);
-                            it.tok_lo = static_cast<int32_t>(pc.pos);
-                            num_entries += it.nq;
-                            for (int i = 0; i < it.nq; ++i)
-                                per_list[static_cast<size_t>(sg->queries[q0 + i]) * kv_heads + h] += 1;
-                            dense_items.push_back(it);
-                        }
+                        const int q0 = job.chunk * q_per_dense;
+                        WorkItem it{};
+                        it.q_off = sg->q_off + q0;
+                        it.nq = std::min(q_per_dense, nq_all - q0);
+                        it.page_off = sg->page_off + static_cast<int32_t>(job.pos / page_size);
+                        it.kv_len = static_cast<int32_t>(job.take);
+                        it.entry_base = num_entries;
+                        it.kv_head = h;
+                        it.cost = static_cast<int32_t>(job.take);
+                        it.tok_lo = static_cast<int32_t>(job.pos);
+                        num_entries += it.nq;
+                        for (int i = 0; i < it.nq; ++i)
+                            per_list[static_cast<size_t>(sg->queries[q0 + i]) * kv_heads + h] += 1;
+                        dense_items.push_back(it);
                     }
                 }
             }
