@@ -368,15 +368,9 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
     for (WorkItem& it : stream_items) it.kv_head = -1;
 
     // ---- 6. dense items: equal work per persistent CTA ------------------------------
-    // The token ranges of the dense segments are laid end to end and cut into `shares` parts of
-    // equal cost.  A share is executed by kv_heads x row_lanes CTAs at the same time
-    // (CTA id = (share * kv_heads + head) * row_lanes + lane): one per KV head and per 128-row
-    // chunk of the queries.  Inside a share every 128-row chunk of every piece goes to the row
-    // lane that has the least work so far: the chunks of one piece land on different lanes and
-    // run side by side (a 2 KB cache row - all heads of a token - is then fetched from HBM within a
-    // short window and the second row chunk finds it in L2), and pieces with a single chunk (few
-    // rows, as in the lower levels of a deep tree) fill both lanes evenly instead of queueing on
-    // the first.
+    // The dense kernel runs `shares` x kv_heads x row_lanes persistent CTAs
+    // (CTA id = (share * kv_heads + head) * row_lanes + lane); every KV head gets the same
+    // placement of (token range, 128-row chunk) jobs on its shares x row_lanes CTAs.
     struct DenseSeg { const Segment* sg; int chunks; };
     std::vector<DenseSeg> dsegs;
     int max_chunks = 1;
