@@ -204,6 +204,26 @@ def reference_scheduler_ms(w, hratio, kv_heads, repeats):
         return None
 
 
+def leave_group(n: int, code: int):
+    """Last barrier and teardown of the process group; exits with `code` when it is not 0.  The
+    teardown runs beside a 30 s timer: a communicator that does not come down (e.g. because a CUDA
+    graph still holds one of its collectives) must not keep a finished run from exiting."""
+    if n > 1:
+        import torch
+        import torch.distributed as dist
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(30.0)
+        if t.is_alive():
+            print("[bench] process group teardown did not finish in 30 s; exiting without it", file=sys.stderr, flush=True)
+            sys.stdout.flush()
+            os._exit(code)
+    if code:
+        sys.exit(code)
+
+
 def main():
     args = parse()
     import numpy as np
@@ -507,7 +527,7 @@ def main():
     # The one optional collective: every rank gets the other ranks' heads (NCCL all-gather into a
     # buffer allocated once, then one small kernel of this library that puts the heads in order).
     # A tensor-parallel model consumes the shard locally instead, so it is not part of `value`;
-    # `value_with_gather` times step + gather as one graph.
+    # `value_with_gather` times the step's graph replay followed by the gather.
     gather_ms = with_gather_ms = 0.0
     if n > 1:
         from pat_b200.sharding import HeadGather
@@ -516,11 +536,11 @@ def main():
             full = hg(out)
         barrier()
         assert tuple(full.shape) == (B, 1, hq * n, D)
-        run_gather = capture(lambda: hg(out))
-        gather_ms = timed(run_gather, 10)
+        # The collective is launched directly, not from a captured graph: a graph that holds an
+        # NCCL collective keeps the communicator's teardown waiting until the graph is destroyed.
+        gather_ms = timed(lambda: hg(out), 10)
         barrier()
-        run_both = capture(lambda: (step(), hg(out)))
-        with_gather_ms = timed(run_both, max(5, min(20, args.steps)))
+        with_gather_ms = timed(lambda: (run_step(), hg(out)), max(5, min(20, args.steps)))
         barrier()
         # the gathered heads of rank r must be rank r's output: check our own block and one neighbour's checksum
         mine = full[:, :, rank * hq:(rank + 1) * hq]
@@ -558,11 +578,7 @@ def main():
                          "attention on the host over the K/V values read back from the GPU"}
 
     if rank != 0:
-        if n > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-        if not parity["ok"]:
-            sys.exit(3)
+        leave_group(n, 0 if parity["ok"] else 3)
         return
 
     peak, peak_kind = measured_peak()
@@ -609,7 +625,7 @@ def main():
                  "stream_tokens_read": hdr.stream_tokens, "dense_tokens_read": hdr.dense_tokens},
         "plan_build_ms": plan_ms,
         **({"all_gather_outputs": {"us": gather_ms * 1e3, "bytes_per_rank": int(out.numel() * elt),
-                                   "note": "optional NCCL all-gather of the output heads + reorder kernel, graph replay; "
+                                   "note": "optional NCCL all-gather of the output heads + reorder kernel, direct launches; "
                                            "not part of value"},
             "value_with_gather": with_gather_ms * 1e3} if n > 1 else {}),
         "append_kv": {"us": append_ms * 1e3, "tokens": B, "bytes": int(2 * 2 * B * hk * D * elt),
@@ -637,12 +653,8 @@ def main():
         ref_ms = reference_scheduler_ms(w, w.group, hk, 5)
         if ref_ms is not None:
             line["plan_build_ms"]["reference_cpp_scheduler_tree_and_pack"] = ref_ms
-    print(json.dumps(line))
-    if n > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if not parity["ok"]:
-        sys.exit(3)
+    print(json.dumps(line), flush=True)
+    leave_group(n, 0 if parity["ok"] else 3)
 
 
 if __name__ == "__main__":

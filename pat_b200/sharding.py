@@ -40,8 +40,11 @@ class HeadGather:
 
     Buffers are allocated once: an NCCL all-gather writes the ranks' ``[B, 1, H/n, D]`` outputs
     rank by rank into a staging buffer and one small kernel of this library puts the heads in
-    order in ``[B, 1, H, D]``.  Nothing synchronises, so a step and its gather can be captured in
-    one CUDA graph.  The result tensor is reused by every call."""
+    order in ``[B, 1, H, D]``.  Nothing here synchronises with the host.  The result tensor is
+    reused by every call.  A caller that captures the gather in a CUDA graph must destroy that
+    graph before the process group: tearing down an NCCL communicator waits for every graph that
+    holds one of its collectives (a 2-GPU run that kept such graphs alive sat in
+    ``destroy_process_group`` until it was killed)."""
 
     def __init__(self, out_shard: torch.Tensor, world: int, group=None):
         b, one, h, d = out_shard.shape
