@@ -398,30 +398,35 @@ int WorkList::finish(std::vector<Segment>& segs, int batch, int hratio, int kv_h
         const int64_t max_shares = std::max<int64_t>(1, opt.num_sms / (static_cast<int64_t>(kv_heads) * row_lanes));
         int64_t share_limit = max_shares;
         if (opt.dense_tile_ns > 0 && header_.stream_tokens > 0) {
-            // Both kernels run at the same time.  The streaming kernel is bound by HBM (about
-            // kStreamPsPerTokenHead per token and KV head: 512 bytes at 6.5 TB/s) and keeps most of
-            // its speed on fewer SMs; the dense kernel is bound by the tensor and special-function
-            // units of the SMs it holds, not by memory.  So the dense kernel gets only the CTAs it
-            // needs to finish within kWindowShare of the time the step's HBM traffic takes, and the
-            // streaming kernel fills the other SMs.  The dense time is estimated as a fixed part
-            // plus (tiles x dense_tile_ns + items x kItemNs) / CTAs, calibrated on a B200.
-            constexpr double kStreamPsPerTokenHead = 79.0, kWindowShare = 0.8;
-            constexpr double kItemNs = 6000.0, kFixedNs = 8000.0;   // per dense item (fill and drain), per launch
-            const double window_ns = static_cast<double>(header_.stream_tokens + header_.dense_unique_tokens) *
-                                     kv_heads * kStreamPsPerTokenHead * 1e-3;
-            {
-                const int64_t group = static_cast<int64_t>(kv_heads) * row_lanes;      // CTAs per share
-                int64_t chunk_sum = 0;
-                for (const DenseSeg& d : dsegs) chunk_sum += d.chunks;
-                int64_t token_chunks = 0;
-                for (const DenseSeg& d : dsegs) token_chunks += d.sg->tokens * d.chunks;
-                const double tile_ns = static_cast<double>(token_chunks) * kv_heads / 128.0 * opt.dense_tile_ns;
-                for (int64_t sh = 1; sh < max_shares; ++sh) {
-                    const double items = static_cast<double>(chunk_sum * kv_heads + sh * group);
-                    if (kFixedNs + (tile_ns + items * kItemNs) / static_cast<double>(sh * group) <= kWindowShare * window_ns) {
-                        share_limit = sh;
-                        break;
-                    }
+            // Both kernels run at the same time: the dense CTAs hold their SMs for as long as they
+            // run, the streaming kernel fills the others and takes every SM over as dense CTAs
+            // retire.  Every dense CTA costs a fixed time and every share adds items, so few CTAs
+            // waste the least SM time - as long as the dense kernel is not what the step waits
+            // for.  The dense kernel therefore gets the fewest shares with which its estimated time
+            // stays below kShare of the estimated step (the streaming kernel alone plus the SM
+            // time the dense CTAs take away from it).  Too few CTAs cost far more than too many,
+            // and the dense kernel is slower beside the streaming kernel than alone: hence the
+            // margin.  Estimates, calibrated on a B200 (kernels timed alone, 4-148 dense CTAs on
+            // five workloads): dense = kFixedNs + (tiles x dense_tile_ns + items x kItemNs) / CTAs;
+            // streaming = kStreamFixedNs + kStreamPsPerTokenHead per token and KV head.
+            constexpr double kStreamPsPerTokenHead = 75.0, kStreamFixedNs = 12000.0, kShare = 0.6;
+            constexpr double kItemNs = 4500.0, kFixedNs = 8000.0;   // per dense item (fill, hand-over, epilogue), per launch
+            const double stream_ns = kStreamFixedNs + static_cast<double>(header_.stream_tokens) * kv_heads *
+                                                          kStreamPsPerTokenHead * 1e-3;
+            const int64_t group = static_cast<int64_t>(kv_heads) * row_lanes;      // CTAs per share
+            int64_t chunk_sum = 0, token_chunks = 0;
+            for (const DenseSeg& d : dsegs) {
+                chunk_sum += d.chunks;
+                token_chunks += d.sg->tokens * d.chunks;
+            }
+            const double tile_ns = static_cast<double>(token_chunks) * kv_heads / 128.0 * opt.dense_tile_ns;
+            for (int64_t sh = 1; sh < max_shares; ++sh) {
+                const double ctas = static_cast<double>(sh * group);
+                const double items = static_cast<double>(chunk_sum * kv_heads) + ctas;     // every share adds about one item per CTA
+                const double dense_ns = kFixedNs + (tile_ns + items * kItemNs) / ctas;
+                if (dense_ns <= kShare * (stream_ns + dense_ns * ctas / opt.num_sms)) {
+                    share_limit = sh;
+                    break;
                 }
             }
         }

@@ -53,9 +53,9 @@ struct WorkOptions {
     int items_per_sm = 4;              // target number of streaming items per SM (all KV heads)
     // Estimated time of one 128-token tile of the dense kernel.  When a work list has streaming
     // work too, the dense kernel runs beside the streaming kernel and gets only as many CTAs as
-    // it needs to finish within the time the streaming kernel needs for its HBM traffic.
+    // keep its estimated time well below the estimated time of the whole step.
     // < 0: the dense kernel is cut for every SM.
-    int dense_tile_ns = 1600;
+    int dense_tile_ns = 1200;
     // Pages of slack behind the page list of a segment that one request owns alone (only in
     // lists built straight from a tree): room for WorkList::advance to append pages in place.
     int grow_slack_pages = 8;
