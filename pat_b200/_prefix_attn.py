@@ -255,8 +255,8 @@ class KernelInfo:
     _FIELDS = ("q_tables", "block_tables", "num_seqs_per_CTAs", "CTA_ranks", "kv_in_CTAs", "MNWs",
                "num_split_per_seq", "max_split_per_seq", "max_seqs_in_CTA", "max_blocks_in_CTA")
 
-    def __init__(self, owner: "PrefixTreeCPP"):
-        self._owner = owner
+    def __init__(self, box: "_TreeBox"):
+        self._box = box             # the native tree and its pack state (not the PrefixTreeCPP: no cycle)
         self._vals = None           # field values, once read
         self._device = None         # where to_gpu sent the plan
         self._work = {}
@@ -283,9 +283,9 @@ class KernelInfo:
 
     def _read(self):
         lib = N.load()
-        o = self._owner
-        o._ensure_packed()
-        h = o._handle
+        o = self._box
+        o.ensure_packed()
+        h = o.handle
         v = dict(q_tables=[], block_tables=[], num_seqs_per_CTAs=[], CTA_ranks=[], kv_in_CTAs=[], MNWs=[])
         view = N.BucketView()
         for i in range(lib.pat_tree_num_buckets(h)):
@@ -298,7 +298,7 @@ class KernelInfo:
             v["kv_in_CTAs"].append(_view_i32(view.kv_in_cta, (view.ctas,)))
         n = C.c_int(0)
         ptr = lib.pat_tree_split_per_seq(h, C.byref(n))
-        v["num_split_per_seq"] = _view_i32(ptr, (n.value,)) if o._packed_once else torch.zeros(0, dtype=torch.int32)
+        v["num_split_per_seq"] = _view_i32(ptr, (n.value,)) if o.packed_once else torch.zeros(0, dtype=torch.int32)
         mx = (C.c_int32 * 3)()
         lib.pat_tree_maxima(h, mx)
         v["max_split_per_seq"], v["max_seqs_in_CTA"], v["max_blocks_in_CTA"] = mx[0], mx[1], mx[2]
@@ -331,10 +331,64 @@ class KernelInfo:
         key = (str(device), cfg.key()) if q_per_req == 1 else (str(device), cfg.key(), int(q_per_req))
         work = self._work.get(key)
         if work is None:
-            o = self._owner
-            work = DeviceWork.from_tree(o._handle, o._hratio, o._kv_heads, device, cfg, q_per_req)
+            o = self._box
+            work = DeviceWork.from_tree(o.handle, o.hratio, o.kv_heads, device, cfg, q_per_req)
             self._work[key] = work
         return work
+
+
+class _TreeBox:
+    """The native tree and the state of its pack, shared by a ``PrefixTreeCPP`` and its
+    ``KernelInfo``.  Neither of the two refers to the other through it, so dropping the last
+    reference frees the native tree at once (a cycle would leave that to the garbage collector, and
+    a decode loop that builds a tree per step would then run every build on fresh memory)."""
+
+    __slots__ = ("handle", "hratio", "kv_heads", "pack_args", "deferred", "built", "packed", "packed_once")
+
+    def __init__(self, handle):
+        self.handle = handle
+        self.hratio = 1
+        self.kv_heads = 8
+        self.pack_args = None           # arguments of the last pack_schedule
+        self.deferred = None            # arguments of a pack that was put off
+        self.built = False
+        self.packed = False             # the native tree holds a plan for its current state
+        self.packed_once = False
+
+    def __del__(self):
+        h = getattr(self, "handle", None)
+        if h:
+            try:
+                N.load().pat_tree_destroy(h)
+            except Exception:
+                pass
+            self.handle = None
+
+    def run_pack(self, args) -> None:
+        arr, hratio, kv_heads, ucm = args
+        ptr, n = (arr.ctypes.data, arr.shape[0]) if arr is not None else (None, 0)
+        rc = N.load().pat_tree_pack(self.handle, ptr, n, hratio, kv_heads, ucm)
+        if rc != 0:
+            raise RuntimeError(f"pack_schedule failed: {N.strerror(rc)}")
+        self.packed = True
+
+    def ensure_packed_before_repack(self) -> None:
+        """A pack that was put off must have happened before the next one accumulates onto it."""
+        if self.packed_once and not self.packed and self.deferred is not None:
+            args, self.deferred = self.deferred, None
+            self.run_pack(args)
+
+    def ensure_packed(self) -> None:
+        """Runs a pack that was put off, or packs again after an in-place advance dropped the plan
+        (same arguments as last time)."""
+        if self.packed or self.pack_args is None:
+            return
+        self.deferred = None
+        self.run_pack(self.pack_args)
+
+
+def _boxed(name):
+    return property(lambda self: getattr(self._box, name), lambda self, v: setattr(self._box, name, v))
 
 
 class PrefixTreeCPP:
@@ -351,26 +405,20 @@ class PrefixTreeCPP:
         lib = N.load()
         self.block_size = int(block_size)
         self.semantics = semantics
-        self._handle = lib.pat_tree_create(self.block_size, 1 if semantics == "cpp" else 0)
-        if not self._handle:
+        handle = lib.pat_tree_create(self.block_size, 1 if semantics == "cpp" else 0)
+        if not handle:
             raise RuntimeError("block_size must be positive")
-        self._kernel_info = KernelInfo(self)
-        self._hratio = 1
-        self._kv_heads = 8
-        self._pack_args = None          # arguments of the last pack_schedule
-        self._deferred = None           # arguments of a pack that was put off
-        self._built = False
-        self._packed = False            # the native tree holds a plan for its current state
-        self._packed_once = False
+        self._box = _TreeBox(handle)
+        self._kernel_info = KernelInfo(self._box)
 
-    def __del__(self):
-        h = getattr(self, "_handle", None)
-        if h:
-            try:
-                N.load().pat_tree_destroy(h)
-            except Exception:
-                pass
-            self._handle = None
+    _handle = _boxed("handle")
+    _hratio = _boxed("hratio")
+    _kv_heads = _boxed("kv_heads")
+    _pack_args = _boxed("pack_args")
+    _deferred = _boxed("deferred")
+    _built = _boxed("built")
+    _packed = _boxed("packed")
+    _packed_once = _boxed("packed_once")
 
     @property
     def kernel_info(self) -> KernelInfo:
@@ -447,26 +495,10 @@ class PrefixTreeCPP:
         self._kernel_info._invalidate()
 
     def _ensure_packed_before_repack(self) -> None:
-        """A pack that was put off must have happened before the next one accumulates onto it."""
-        if self._packed_once and not self._packed and self._deferred is not None:
-            args, self._deferred = self._deferred, None
-            self._run_pack(args)
+        self._box.ensure_packed_before_repack()
 
     def _ensure_packed(self) -> None:
-        """Runs a pack that was put off, or packs again after an in-place advance dropped the plan
-        (same arguments as last time)."""
-        if self._packed or self._pack_args is None:
-            return
-        self._deferred = None
-        self._run_pack(self._pack_args)
-
-    def _run_pack(self, args) -> None:
-        arr, hratio, kv_heads, ucm = args
-        ptr, n = (arr.ctypes.data, arr.shape[0]) if arr is not None else (None, 0)
-        rc = N.load().pat_tree_pack(self._handle, ptr, n, hratio, kv_heads, ucm)
-        if rc != 0:
-            raise RuntimeError(f"pack_schedule failed: {N.strerror(rc)}")
-        self._packed = True
+        self._box.ensure_packed()
 
     def advance(self, seq_lens, block_table: torch.Tensor, device=None) -> bool:
         """One decode step later: the same requests, each at least as long as before, each table row

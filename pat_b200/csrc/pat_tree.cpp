@@ -146,14 +146,14 @@ int Tree::build_padded(const int32_t* seq_lens, const int32_t* table, int num_se
     }
     const size_t base = pool_.size();
     if (base != 0) return kTreeBadArgument;  // one build per tree object
-    pool_.resize(total);
+    pool_.reserve(total);               // filled by appending: no zero-fill of a megabyte first
     size_t pos = 0;
     nodes_.reserve(static_cast<size_t>(num_seqs) * 2 + 1);
     std::vector<size_t> starts(num_seqs);
     for (int i = 0; i < num_seqs; ++i) {
         starts[i] = pos;
-        std::copy(table + static_cast<size_t>(i) * row_stride,
-                  table + static_cast<size_t>(i) * row_stride + counts[i], pool_.begin() + pos);
+        const int32_t* row = table + static_cast<size_t>(i) * row_stride;
+        pool_.insert(pool_.end(), row, row + counts[i]);
         pos += counts[i];
     }
     leaf_.assign(num_seqs, 0);

@@ -2,6 +2,7 @@
 decode steps.  All on the CPU: trees and plans are compared with fresh builds (bit for bit, both
 scheduler semantics) and work lists are executed item by item with the fp32 oracle."""
 import ctypes as C
+import sys
 
 import numpy as np
 import pytest
@@ -231,6 +232,32 @@ def test_kernel_info_is_only_materialised_when_read(native_lib):
     assert info._vals is None                       # nothing has asked for the plan tensors yet
     assert info.max_split_per_seq >= 1 and len(info.q_tables) == len(info.MNWs) > 0
     assert info._vals is not None and info.num_split_per_seq.shape[0] == w.batch
+
+
+def test_a_dropped_tree_is_freed_at_once_and_its_plan_stays_readable(native_lib):
+    """``PrefixTreeCPP`` and its ``kernel_info`` share the native tree through a holder neither of
+    them reaches the other by: no reference cycle, so a decode loop that builds a tree per step
+    hands the native memory back with the last reference, not at the next garbage collection."""
+    import gc
+    import weakref
+    w = scaled_down(3, 4)
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        tree = PrefixTreeCPP(w.page_size)
+        tree.build_radix_tree(list(w.seq_lens), torch.from_numpy(w.padded_table()))
+        tree.pack_schedule(None, w.group, w.num_kv_heads)
+        info, gone = tree.kernel_info, weakref.ref(tree)
+        del tree
+        assert gone() is None
+        assert len(info.q_tables) == len(info.MNWs) > 0         # the put-off pack still runs
+        holder = info._box
+        assert holder.handle
+        del info
+        assert sys.getrefcount(holder) == 2                     # this name and the call's argument
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 # ---------------------------------------------------------------------------------------------
