@@ -49,7 +49,11 @@ struct WorkOptions {
     int dense_min_rows = 17;           // segments with at least this many rows go to the dense kernel
     int chunk_tokens_min = 256;
     int chunk_tokens_max = 2048;
-    int dense_piece_tokens_min = 512;  // a dense share is not cut (much) below this many tokens
+    // A dense share is not cut (much) below this many tokens.  Two tiles: with 512 a rank of a 4-
+    // or 8-GPU run on a short batch left most SMs without dense work (22.7 vs 26.0 us per step on
+    // one rank of four of the two-level tree); with 128 the extra partial rows cost the merge more
+    // than the dense kernel gains.
+    int dense_piece_tokens_min = 256;
     int items_per_sm = 4;              // target number of streaming items per SM (all KV heads)
     // Estimated time of one 128-token tile of the dense kernel.  When a work list has streaming
     // work too, the dense kernel runs beside the streaming kernel and gets only as many CTAs as
