@@ -244,6 +244,16 @@ def test_dense_share_of_the_sms(native_lib):
         assert counts[800] <= counts[1600] <= counts[3200] <= counts[-1]
         assert counts[1600] < counts[-1]
         assert counts[-1] > 148 - 2 * hk * 2             # all SMs, up to one group of CTAs
+    # a short step (one 4096-token prefix, 64 suffixes): the dense kernel keeps clear of the step's
+    # critical path with a part of the SMs, and still gets enough CTAs that a CTA has few tiles
+    w1 = make_config(1)
+    t1 = PrefixTree(w1.page_size)
+    t1.build_radix_tree(list(w1.seq_lens), [list(r) for r in w1.block_tables])
+    header, blob = W.build_work(_plan_lists(t1.pack_schedule(None, w1.group, w1.num_kv_heads)), w1.batch, w1.group,
+                                w1.num_kv_heads, w1.page_size)
+    assert 32 <= header.num_dense_ctas <= 96
+    header, blob = W.build_work(_plan_lists(t1.pack_schedule(None, w1.group, 1)), w1.batch, w1.group, 1, w1.page_size)
+    assert 16 <= header.num_dense_ctas <= 64                 # one rank of eight: pieces of two tiles at least
     # dense work only (every request shares everything): no streaming kernel to run beside
     lens = [4096] * 64
     tables = [list(range(256))] * 64
